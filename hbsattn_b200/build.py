@@ -1,0 +1,56 @@
+"""Builds libhbsattn_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
+
+    python hbsattn_b200/build.py [--force] [--verbose]     (run as a script: importing the package needs the library)
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_PATH = os.path.join(PKG_DIR, "libhbsattn_b200.so")
+SOURCES = ["hbsa_api.cu", "hbsa_schedule.cu", "hbsa_fwd_generic.cu", "hbsa_fwd_sm100.cu"]
+HEADERS = ["hbsa_common.cuh", "sm100_ptx.cuh", os.path.join("..", "..", "include", "hbsattn_b200.h")]
+
+
+def _nvcc() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; hbsattn_b200 has no CPU fallback and cannot be built without CUDA")
+    return cand
+
+
+def nvcc_flags(verbose: bool = False):
+    flags = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+             "-Xcompiler", "-fPIC", "-I", os.path.join(PKG_DIR, "..", "include")]
+    if verbose:
+        flags += ["-Xptxas", "-v"]
+    return flags
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every CUDA source into hbsattn_b200/libhbsattn_b200.so; returns its path."""
+    if not force and not is_stale():
+        return LIB_PATH
+    cmd = [_nvcc(), "-shared", "-o", LIB_PATH] + nvcc_flags(verbose) + [os.path.join(CSRC, s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libhbsattn_b200.so (exit %d)" % res.returncode)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

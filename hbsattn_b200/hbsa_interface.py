@@ -1,0 +1,190 @@
+"""Operator API of the block-sparse attention forward.
+
+Same callable, same positional arguments, same assertions and exception types as the
+reference's ``hbsattn/hbsa_interface.py:6-35``; the body hands raw pointers, strides and sizes
+to ``hbsa_forward`` of the C ABI, which builds the block metadata and the work schedule on the
+device and runs the sm_100a attention kernel on torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.HBSA_DTYPE_BF16, torch.float16: _lib.HBSA_DTYPE_F16, torch.float32: _lib.HBSA_DTYPE_F32}
+_IMPLS = {"auto": _lib.HBSA_IMPL_AUTO, "generic": _lib.HBSA_IMPL_GENERIC, "sm100": _lib.HBSA_IMPL_SM100}
+
+_state = {"impl": os.environ.get("HBSATTN_B200_IMPL", "auto"), "last_workspace": None}
+
+
+def set_kernel_family(name: str) -> None:
+    """``'auto'`` (default), ``'sm100'`` (tcgen05 kernel, error if ineligible) or ``'generic'``."""
+    if name not in _IMPLS:
+        raise ValueError(f"Invalid kernel family: {name}")
+    _state["impl"] = name
+
+
+def _validate_default() -> bool:
+    return os.environ.get("HBSATTN_B200_VALIDATE", "1") != "0"
+
+
+def read_status(workspace: torch.Tensor):
+    """Synchronises and returns the 16 device status words of a forward's workspace."""
+    lib = _lib.load()
+    out = (ctypes.c_int32 * _lib.STATUS_WORDS)()
+    with torch.cuda.device(workspace.device):
+        stream = torch.cuda.current_stream(workspace.device).cuda_stream
+        rc = lib.hbsa_read_status(workspace.data_ptr(), ctypes.cast(out, ctypes.c_void_p), stream)
+    if rc != 0:
+        raise RuntimeError(f"hbsa_read_status failed ({rc}): {_lib.last_error()}")
+    return list(out)
+
+
+def last_status():
+    """Status words of the most recent forward on this process (synchronises)."""
+    ws = _state["last_workspace"]
+    return read_status(ws) if ws is not None else [0] * _lib.STATUS_WORDS
+
+
+def make_args(q, k, v, out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
+              softmax_scale, num_q_block, num_k_block, workspace, impl):
+    a = _lib.ForwardArgs()
+    a.struct_bytes = ctypes.sizeof(_lib.ForwardArgs)
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.o = out.data_ptr() if out is not None else None
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", out if out is not None else q)):
+        arr = getattr(a, name)
+        for i in range(3):
+            arr[i] = t.stride(i)
+    a.cu_q_seqlens = cu_q_seqlens.data_ptr()
+    a.cu_k_seqlens = cu_k_seqlens.data_ptr()
+    a.block_mask = block_mask.data_ptr()
+    for i in range(3):
+        a.mask_stride[i] = block_mask.stride(i)          # bool: one byte per element
+    a.total_q, a.total_k = q.shape[0], k.shape[0]
+    a.nhead_q, a.nhead_k, a.headdim = q.shape[1], k.shape[1], q.shape[2]
+    a.batch = cu_q_seqlens.numel() - 1
+    a.num_q_block, a.num_k_block = int(num_q_block), int(num_k_block)
+    a.q_block_size, a.k_block_size = int(q_block_size), int(k_block_size)
+    a.causal = 1 if causal else 0
+    a.use_default_scale = 1 if softmax_scale is None else 0
+    a.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
+    a.dtype = _DTYPES[q.dtype]
+    a.impl = impl
+    a.workspace = workspace.data_ptr()
+    a.workspace_bytes = workspace.numel()
+    return a
+
+
+def _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask):
+    if not (q.is_cuda and k.is_cuda and v.is_cuda and block_mask.is_cuda and cu_q_seqlens.is_cuda and cu_k_seqlens.is_cuda):
+        raise RuntimeError("hbsattn_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
+    assert q.ndim == 3 and k.ndim == 3 and v.ndim == 3, "q, k, v must be (seqlen, nhead, headdim)"
+    assert q.dtype == k.dtype == v.dtype and q.dtype in _DTYPES, "q, k, v must share a dtype of bfloat16, float16 or float32"
+    assert k.shape == v.shape and q.shape[2] == k.shape[2], "k and v must have the same shape and q's headdim"
+    assert len(cu_q_seqlens) == len(cu_k_seqlens) and cu_q_seqlens.ndim == 1 and cu_k_seqlens.ndim == 1, \
+        "cu_q_seqlens and cu_k_seqlens must be 1D tensors of same length"
+    if cu_q_seqlens.dtype != torch.int32:
+        cu_q_seqlens = cu_q_seqlens.to(torch.int32)
+    if cu_k_seqlens.dtype != torch.int32:
+        cu_k_seqlens = cu_k_seqlens.to(torch.int32)
+    return cu_q_seqlens.contiguous(), cu_k_seqlens.contiguous()
+
+
+def alloc_workspace(nhead_k, num_q_block, num_k_block, batch, device) -> torch.Tensor:
+    nbytes = _lib.load().hbsa_workspace_bytes(nhead_k, num_q_block, num_k_block, batch)
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)     # torch's CUDA allocations are 512-byte aligned
+
+
+class _HBSAttentionFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
+                softmax_scale, tile_mode='auto', num_q_block=None, cu_q_block=None, q_block_to_batch=None,
+                cu_num_q_block=None, num_k_block=None, cu_k_block=None, k_block_to_batch=None, cu_num_k_block=None):
+        """``q``: (total_q, nhead_q, headdim); ``k``, ``v``: (total_k, nhead_k, headdim), packed varlen.
+        ``block_mask``: bool (nhead_k, num_q_block, num_k_block) over global block indices.
+        The eight trailing arguments are the outputs of ``calculate_blocks`` for q and k; they are
+        accepted for compatibility (``test/test_accuracy.py:72``) - only the two block counts are used,
+        the tables themselves are rebuilt on the device from ``cu_*_seqlens``.
+        Returns a contiguous (total_q, nhead_q, headdim) tensor in ``q``'s dtype.
+        """
+        have_meta = not (num_q_block is None or cu_q_block is None or q_block_to_batch is None or cu_num_q_block is None
+                         or num_k_block is None or cu_k_block is None or k_block_to_batch is None or cu_num_k_block is None)
+        assert block_mask.dtype == torch.bool, "block_mask must be a boolean tensor"
+        assert block_mask.ndim == 3, "block_mask must have shape (nheads_k, num_q_block, num_k_block)"
+        if have_meta:
+            assert block_mask.shape == (k.shape[1], num_q_block, num_k_block), \
+                f"block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block) = ({k.shape[1]}, {num_q_block}, {num_k_block})"
+        else:
+            assert block_mask.shape[0] == k.shape[1], \
+                f"block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block); nheads_k = {k.shape[1]}"
+            num_q_block, num_k_block = block_mask.shape[1], block_mask.shape[2]
+
+        if tile_mode == 'auto':
+            pass
+        elif tile_mode == 'fix':
+            assert (q_block_size & (q_block_size - 1) == 0) and (k_block_size & (k_block_size - 1) == 0), \
+                "q_block_size and k_block_size must be powers of 2"
+        else:
+            raise ValueError(f"Invalid tile mode: {tile_mode}")
+
+        assert q.shape[1] % k.shape[1] == 0, "nhead_q must be divisible by nhead_k (for GQA)"
+        assert q_block_size % 16 == 0 and k_block_size % 16 == 0 and q_block_size > 0 and k_block_size > 0, \
+            "q_block_size and k_block_size must be integer multiples of 16."
+
+        cu_q32, cu_k32 = _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask)
+        lib = _lib.load()
+        dev = q.device
+        with torch.cuda.device(dev):
+            out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+            if q.shape[0] == 0:
+                return out
+            ws = alloc_workspace(k.shape[1], num_q_block, num_k_block, cu_q32.numel() - 1, dev)
+            args = make_args(q, k, v, out, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, softmax_scale,
+                             num_q_block, num_k_block, ws, _IMPLS[_state["impl"]])
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            rc = lib.hbsa_forward(ctypes.byref(args), stream)
+            if rc != 0:
+                raise RuntimeError(f"hbsa_forward failed ({rc}): {_lib.last_error()}")
+            _state["last_workspace"] = ws
+            if not have_meta and _validate_default():
+                # The reference computes the block tables here (one host sync) and asserts the mask
+                # shape against them (hbsa_interface.py:14-20); the device did the same check.
+                status = read_status(ws)
+                assert status[0] != _lib.HBSA_STATUS_BLOCK_COUNT_MISMATCH, \
+                    f"block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block) = ({k.shape[1]}, {status[1]}, {status[2]})"
+                if status[0] != _lib.HBSA_STATUS_OK:
+                    raise RuntimeError(f"hbsa_forward: device status {status[0]} (work item {status[3]})")
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        raise NotImplementedError("It does not support gradient propagation yet")
+
+
+HBSAttention = _HBSAttentionFunction.apply
+
+
+def block_decisions(q, k, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal):
+    """The valid/skip decision of every (kv-head, q-block, k-block) pair as the forward takes it:
+    returns ``(decisions bool [nhead_k, num_q_block, num_k_block], counts int32 [nhead_k, num_q_block])``."""
+    cu_q32, cu_k32 = _prepare(q, k, k, cu_q_seqlens, cu_k_seqlens, block_mask)
+    lib = _lib.load()
+    dev = q.device
+    nhk, nqb, nkb = block_mask.shape
+    with torch.cuda.device(dev):
+        ws = alloc_workspace(nhk, nqb, nkb, cu_q32.numel() - 1, dev)
+        args = make_args(q, k, k, None, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, 1.0,
+                         nqb, nkb, ws, _lib.HBSA_IMPL_AUTO)
+        dec = torch.empty((nhk, nqb, nkb), dtype=torch.uint8, device=dev)
+        counts = torch.empty((nhk, nqb), dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = lib.hbsa_block_decisions(ctypes.byref(args), dec.data_ptr(), counts.data_ptr(), stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_block_decisions failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+    return dec.bool(), counts

@@ -1,0 +1,167 @@
+/*
+ * hbsattn_b200 - C ABI of the B200 (sm_100a) heterogeneous block-sparse attention forward.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; no torch
+ * types cross this boundary.  All work is enqueued on the CUDA stream passed as the
+ * last argument (a cudaStream_t cast to void*; NULL = the legacy default stream) of the
+ * device that is current when the call is made.  No entry point synchronises the
+ * stream except hbsa_read_status().
+ *
+ * Return value of every int function: 0 = enqueued; negative = the arguments were
+ * rejected before any launch (text in hbsa_last_error()); positive = a CUDA runtime
+ * error code observed while launching.
+ */
+#ifndef HBSATTN_B200_H_
+#define HBSATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HBSA_ABI_VERSION 1
+
+/* Element type of q, k, v and o. */
+enum { HBSA_DTYPE_BF16 = 0, HBSA_DTYPE_F16 = 1, HBSA_DTYPE_F32 = 2 };
+
+/* Kernel family. AUTO picks the tcgen05 kernel whenever the problem is eligible
+ * (bf16/fp16, headdim 64 or 128, unit stride along headdim, 16-byte aligned rows,
+ * softmax_scale > 0) and the generic CUDA-core kernel otherwise.  Forcing SM100 on an
+ * ineligible problem is an argument error.  Both families are CUDA; there is no CPU path. */
+enum { HBSA_IMPL_AUTO = 0, HBSA_IMPL_GENERIC = 1, HBSA_IMPL_SM100 = 2 };
+
+/* Argument errors (negative return values). */
+enum {
+  HBSA_ERR_NULL = -1,        /* a required pointer is NULL                                  */
+  HBSA_ERR_SHAPE = -2,       /* a size is not positive, or nhead_q % nhead_k != 0            */
+  HBSA_ERR_BLOCK_SIZE = -3,  /* q/k block size is not a positive multiple of 16             */
+  HBSA_ERR_DTYPE = -4,       /* unknown dtype / impl enum                                   */
+  HBSA_ERR_WORKSPACE = -5,   /* workspace smaller than hbsa_workspace_bytes()               */
+  HBSA_ERR_UNSUPPORTED = -6, /* HBSA_IMPL_SM100 forced on a problem it cannot run           */
+  HBSA_ERR_DRIVER = -7,      /* the CUDA driver entry point for tensor maps is unavailable  */
+  HBSA_ERR_STRUCT = -8       /* struct_bytes does not match this library                    */
+};
+
+/* Device-side status word (read back with hbsa_read_status). */
+enum {
+  HBSA_STATUS_OK = 0,
+  HBSA_STATUS_BLOCK_COUNT_MISMATCH = 1, /* num_q_block/num_k_block differ from what cu_seqlens imply;
+                                           the attention kernel did not run                       */
+  HBSA_STATUS_WAIT_LIMIT = 2            /* a bounded wait inside the attention kernel ran out       */
+};
+
+/* Library / ABI version (HBSA_ABI_VERSION of the build). */
+int hbsa_version(void);
+
+/* Text of the last argument or launch error on the calling thread. */
+const char* hbsa_last_error(void);
+
+/*
+ * Block tables of a packed varlen batch, built on the device.
+ * Replaces hbsattn/utils.py:7-50 (calculate_blocks), which issues ~12 torch launches.
+ *
+ *   cu_seqlen      int32[batch+1]  device, cumulative sequence lengths
+ *   capacity       number of block entries the two block arrays can hold
+ *   cu_block       int32[capacity+1] device or NULL: token offset of every block boundary
+ *                  (relative to cu_seqlen[0], like the reference's cumsum at utils.py:37)
+ *   block_to_batch int32[capacity]   device or NULL: sample index of every block (utils.py:39-43)
+ *   cu_num_block   int32[batch+1]    device: first block index of every sample (utils.py:17-24)
+ *
+ * Entries beyond `capacity` are not written.  Call it once with capacity 0 to learn
+ * cu_num_block[batch] (the reference also needs this one host read, utils.py:27).
+ */
+int hbsa_calculate_blocks(const int32_t* cu_seqlen, int batch, int block_size, int capacity,
+                          int32_t* cu_block, int32_t* block_to_batch, int32_t* cu_num_block,
+                          void* stream);
+
+/* Bytes of scratch device memory hbsa_forward / hbsa_block_decisions need for a mask of
+ * shape (nhead_k, num_q_block, num_k_block) and `batch` samples.  Depends on nothing else. */
+size_t hbsa_workspace_bytes(int nhead_k, int num_q_block, int num_k_block, int batch);
+
+/*
+ * One forward call.  Replaces hbsattn/hbsa_interface.py:9-27 together with the launchers
+ * and Triton kernels behind it (fwd_triton_auto_tile_size.py:254-310 and :76-251,
+ * fwd_triton_fix_tile_size.py:216-276 and :30-212).
+ *
+ * Layout: q,o are [total_q, nhead_q, headdim]; k,v are [total_k, nhead_k, headdim]; packed
+ * varlen, strides in ELEMENTS for (token, head, dim).  block_mask is bool bytes of shape
+ * [nhead_k, num_q_block, num_k_block] over GLOBAL block indices with strides in BYTES;
+ * entries that pair blocks of different samples are ignored.  cu_*_seqlens are int32[batch+1]
+ * on the device.  Causal masking is aligned bottom-right when k_len != q_len.
+ * use_default_scale != 0 selects headdim^-0.5 (the reference's softmax_scale=None) and ignores
+ * softmax_scale.
+ */
+typedef struct hbsa_forward_args {
+  size_t struct_bytes;            /* sizeof(hbsa_forward_args) of the caller                 */
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  int64_t q_stride[3];
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  const int32_t* cu_q_seqlens;
+  const int32_t* cu_k_seqlens;
+  const uint8_t* block_mask;
+  int64_t mask_stride[3];
+  int32_t total_q;
+  int32_t total_k;
+  int32_t nhead_q;
+  int32_t nhead_k;
+  int32_t headdim;
+  int32_t batch;
+  int32_t num_q_block;
+  int32_t num_k_block;
+  int32_t q_block_size;
+  int32_t k_block_size;
+  int32_t causal;
+  int32_t use_default_scale;
+  float softmax_scale;
+  int32_t dtype;                  /* HBSA_DTYPE_*                                            */
+  int32_t impl;                   /* HBSA_IMPL_*                                             */
+  int32_t reserved;
+  void* workspace;                /* >= hbsa_workspace_bytes(...) bytes, 256-byte aligned    */
+  size_t workspace_bytes;
+} hbsa_forward_args;
+
+int hbsa_forward(const hbsa_forward_args* args, void* stream);
+
+/*
+ * The two halves of hbsa_forward, for callers that reuse one mask over several calls (layers,
+ * decode steps) the way the reference's callers reuse calculate_blocks outputs
+ * (test/test_speedup.py:100-102,152).
+ *   hbsa_build_schedule: block tables from cu_*_seqlens, active k-block count of every
+ *       (kv-head, q-block) row, rows ordered by descending work - all into `workspace`
+ *       (q, k, v, o are not read and may be NULL).
+ *   hbsa_attention: the attention kernel alone; `workspace` must hold the schedule built from the
+ *       same cu_*_seqlens, block_mask, block sizes and causal flag.
+ */
+int hbsa_build_schedule(const hbsa_forward_args* args, void* stream);
+int hbsa_attention(const hbsa_forward_args* args, void* stream);
+
+/*
+ * The per-block valid/skip decision the forward uses, for checking and FLOP accounting.
+ * Same arguments as hbsa_forward (q,k,v,o may be NULL).  Writes
+ *   decisions  uint8[nhead_k * num_q_block * num_k_block]  1 = the block pair is computed
+ *   counts     int32[nhead_k * num_q_block] or NULL         active k-blocks per (kv-head, q-block)
+ * The rule is the block-level consequence of the element mask of hbsattn/reference.py:56-89.
+ */
+int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int32_t* counts,
+                         void* stream);
+
+/* Which kernel family hbsa_forward would run for these arguments: HBSA_IMPL_GENERIC or
+ * HBSA_IMPL_SM100 (or a negative argument error). Launches nothing. */
+int hbsa_select_impl(const hbsa_forward_args* args);
+
+/* Copies the 16 device status words of `workspace` (word 0 = HBSA_STATUS_*, words 1.. = detail)
+ * to status_out[0..15].  Synchronises `stream`.  For tests and debugging; the hot path never
+ * calls it. */
+int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HBSATTN_B200_H_ */
