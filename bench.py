@@ -35,6 +35,8 @@ WORKLOADS = {
     # name: batch, (q_lo, q_hi, q_round), k spec, nhead_q, nhead_k, headdim, qbs, kbs, causal, p_keep, force
     "cfg2": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
                  p=0.1, force="diag", desc="B8 x 8192 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.1 + diagonal"),
+    "cfg2_b2": dict(batch=2, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
+                    p=0.1, force="diag", desc="profiling cut of cfg2: B2 x 8192 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.1 + diagonal"),
     "cfg2_s0.7": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
                       p=0.3, force="diag", desc="B8 x 8192 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.3 + diagonal"),
     "cfg3": dict(batch=8, q_len=(1024, 16384, 16), k_len="same", hq=32, hk=8, d=128, qbs=80, kbs=48, causal=False,
