@@ -28,7 +28,9 @@ EXPORTED_SYMBOLS = (
     "hbsa_block_decisions",
     "hbsa_select_impl",
     "hbsa_read_status",
+    "hbsa_forward_static_scratch",
 )
+STATIC_SCRATCH_BYTES = 4 << 20
 
 
 class ForwardArgs(ctypes.Structure):
@@ -105,6 +107,8 @@ def load() -> ctypes.CDLL:
         lib.hbsa_select_impl.argtypes = [ctypes.POINTER(ForwardArgs)]
         lib.hbsa_read_status.restype = i32
         lib.hbsa_read_status.argtypes = [vp, vp, vp]
+        lib.hbsa_forward_static_scratch.restype = i32
+        lib.hbsa_forward_static_scratch.argtypes = [ctypes.POINTER(ForwardArgs), vp]
         if lib.hbsa_version() != 1:
             raise ImportError("libhbsattn_b200.so was built from a different ABI version")
         _lib = lib

@@ -12,7 +12,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libhbsattn_b200.so")
-SOURCES = ["hbsa_api.cu", "hbsa_schedule.cu", "hbsa_fwd_generic.cu", "hbsa_fwd_sm100.cu"]
+SOURCES = ["hbsa_api.cu", "hbsa_schedule.cu", "hbsa_fwd_generic.cu", "hbsa_fwd_sm100.cu",
+           "hbsa_static_scratch.cu"]
 HEADERS = ["hbsa_common.cuh", "sm100_ptx.cuh", os.path.join("..", "..", "include", "hbsattn_b200.h")]
 
 

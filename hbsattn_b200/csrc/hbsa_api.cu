@@ -1,5 +1,6 @@
 // extern "C" entry points of libhbsattn_b200 (declared in include/hbsattn_b200.h).
 #include <math.h>
+#include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
 
@@ -74,6 +75,15 @@ int select_impl(const hbsa_forward_args* a, const hbsa::Problem& p) {
 }
 
 }  // namespace
+
+namespace hbsa {
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+}  // namespace hbsa
 
 extern "C" {
 

@@ -81,6 +81,9 @@ __device__ __forceinline__ RowGeom row_geometry(const Problem& p, const int32_t*
   return g;
 }
 
+// printf-style setter of the text hbsa_last_error() returns on the calling thread.
+void set_last_error(const char* fmt, ...);
+
 // Launchers (each enqueues on `stream` and returns the cudaError_t of the launch).
 cudaError_t launch_calculate_blocks(const int32_t* cu_seqlen, int batch, int block_size, int capacity,
                                     int32_t* cu_block, int32_t* block_to_batch, int32_t* cu_num_block,

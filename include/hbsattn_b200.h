@@ -161,6 +161,26 @@ int hbsa_select_impl(const hbsa_forward_args* args);
  * calls it. */
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
 
+/*
+ * hbsa_forward for callers that cannot allocate: identical to hbsa_forward except that the
+ * scratch memory is a fixed array inside the library instead of `args->workspace` (which is
+ * ignored, as is `workspace_bytes`; both may be 0).  It has no counterpart in the reference - it
+ * exists for hosts that own all device memory themselves and give a plug-in only its inputs and
+ * outputs (an inference server with a pre-reserved arena, an execute callback that bans
+ * cudaMalloc).  The call allocates nothing, on the host side of CUDA or on the device.
+ *
+ *  - Limit: hbsa_workspace_bytes(nhead_k, num_q_block, num_k_block, batch) must not exceed
+ *    HBSA_STATIC_SCRATCH_BYTES (about nhead_k * num_q_block <= 500k rows); larger problems
+ *    return HBSA_ERR_WORKSPACE and hbsa_last_error() says how many bytes were needed.
+ *  - Cost: every GPU that loads the library carries the array until the process exits.
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the array.  Each call re-initialises what it needs, so
+ *    back-to-back calls on one stream are fine; calls that may overlap on the GPU race.
+ */
+#define HBSA_STATIC_SCRATCH_BYTES (4u << 20)
+int hbsa_forward_static_scratch(const hbsa_forward_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
