@@ -384,13 +384,13 @@ def ours_arm(args):
             "config": {"workload": f"{args.workload}: {w['desc']}", "per_gpu": "every rank runs the whole workload with its own seed",
                        "active_block_pairs_per_gpu": active_pairs, "flop_per_step_per_gpu": flops,
                        "l2": "q+k+v+o exceed the 126 MB L2; no flush", "kernel_family": {1: "generic", 2: "sm100"}.get(family, str(family)),
-                       "step": "schedule build (5 small kernels) + attention kernel"},
+                       "step": "schedule build (3 small kernels) + attention kernel"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": None, "kernel": "fwd_sm100_kernel" if family == 2 else "fwd_generic_kernel",
                          "kernel_ms": kern_ms, "peak_source": peak_kind},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
-            "gpu_launches": 6 * args.steps,
+            "gpu_launches": 4 * args.steps,
             "clocks": sampler.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:

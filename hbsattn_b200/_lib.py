@@ -29,6 +29,8 @@ EXPORTED_SYMBOLS = (
     "hbsa_select_impl",
     "hbsa_read_status",
     "hbsa_forward_static_scratch",
+    "hbsa_debug_trace_bytes",
+    "hbsa_debug_set_trace",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -109,6 +111,10 @@ def load() -> ctypes.CDLL:
         lib.hbsa_read_status.argtypes = [vp, vp, vp]
         lib.hbsa_forward_static_scratch.restype = i32
         lib.hbsa_forward_static_scratch.argtypes = [ctypes.POINTER(ForwardArgs), vp]
+        lib.hbsa_debug_trace_bytes.restype = ctypes.c_size_t
+        lib.hbsa_debug_trace_bytes.argtypes = []
+        lib.hbsa_debug_set_trace.restype = None
+        lib.hbsa_debug_set_trace.argtypes = [vp]
         if lib.hbsa_version() != 1:
             raise ImportError("libhbsattn_b200.so was built from a different ABI version")
         _lib = lib

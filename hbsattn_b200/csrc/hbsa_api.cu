@@ -58,6 +58,7 @@ int make_problem(const hbsa_forward_args* a, bool need_tensors, hbsa::Problem* p
   p->kbs = a->k_block_size;
   p->causal = a->causal ? 1 : 0;
   p->scale = a->use_default_scale ? 1.0f / sqrtf((float)a->headdim) : a->softmax_scale;
+  p->kv_tile = hbsa::sm100_kv_tile_rows(a->k_block_size);
   return 0;
 }
 
@@ -120,7 +121,7 @@ int hbsa_build_schedule(const hbsa_forward_args* args, void* stream_) {
   if (rc != 0) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   hbsa::Workspace ws = hbsa::make_workspace(args->workspace, p.nhead_k, p.num_q_block, p.num_k_block, p.batch);
-  cudaError_t e = hbsa::launch_schedule(p, ws, nullptr, true, stream);
+  cudaError_t e = hbsa::launch_schedule(p, ws, nullptr, stream);
   return e == cudaSuccess ? 0 : fail_cuda(e, "hbsa_build_schedule");
 }
 
@@ -161,7 +162,7 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   hbsa::Workspace ws = hbsa::make_workspace(args->workspace, p.nhead_k, p.num_q_block, p.num_k_block, p.batch);
   cudaError_t e = cudaMemsetAsync(decisions, 0, (size_t)p.nhead_k * p.num_q_block * p.num_k_block, stream);
   if (e != cudaSuccess) return fail_cuda(e, "hbsa_block_decisions (memset)");
-  e = hbsa::launch_schedule(p, ws, decisions, false, stream);
+  e = hbsa::launch_schedule(p, ws, decisions, stream);
   if (e != cudaSuccess) return fail_cuda(e, "hbsa_block_decisions");
   if (counts) {
     e = cudaMemcpyAsync(counts, ws.counts, (size_t)p.nhead_k * p.num_q_block * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream);
@@ -169,6 +170,10 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   }
   return 0;
 }
+
+size_t hbsa_debug_trace_bytes(void) { return hbsa::sm100_trace_bytes(); }
+
+void hbsa_debug_set_trace(void* device_buffer) { hbsa::sm100_set_trace(static_cast<long long*>(device_buffer)); }
 
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream_) {
   if (!workspace || !status_out) return fail(HBSA_ERR_NULL, "workspace and status_out must not be NULL");

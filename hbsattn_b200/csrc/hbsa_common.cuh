@@ -11,8 +11,8 @@
 
 namespace hbsa {
 
-constexpr int kHistBins = 1024;      // work items are bucketed by min(active k-blocks, kHistBins-1)
 constexpr int kStatusWords = 16;
+constexpr int kItemWords = 12;       // int32 words of one ItemRecord
 
 // Carved out of the caller's workspace by make_workspace(); every pointer is a device pointer.
 struct Workspace {
@@ -21,11 +21,23 @@ struct Workspace {
   int32_t* cnk;          // [batch+1] first k-block of every sample
   int32_t* qb2b;         // [num_q_block] sample of every q-block
   int32_t* counts;       // [nhead_k*num_q_block] active k-blocks per (kv-head, q-block) row
-  int32_t* order;        // [nhead_k*num_q_block] rows sorted by descending count (bucketed)
-  int32_t* hist;         // [kHistBins]
-  int32_t* bin_start;    // [kHistBins]
-  int32_t* bin_cursor;   // [kHistBins]
+  int32_t* items;        // [nhead_k*num_q_block][kItemWords] ItemRecord of every row, in launch order
+  int32_t* cursor;       // [64] word 0: next work item of the persistent attention kernel
+  int32_t* qpos;         // [batch] launch position (in q-blocks) of every sample inside a kv-head
 };
+
+// Everything the attention kernel needs to know about one (kv-head, q-block) row, written once by
+// the schedule kernel so that a CTA fetches its next piece of work with a single 48-byte load.
+// Launch order: kv-head major, then samples from the longest k_len to the shortest, and inside a
+// sample the q-blocks from last to first (under a causal mask the longest rows come first), so the
+// queue drains on short rows and the CTAs that run at the same time share the K/V of a few
+// (sample, kv-head) units in L2.
+struct __align__(16) ItemRecord {
+  int hk, qb, q_begin, q_end;        // kv-head, q-block, token range of the q-block (global)
+  int q_in0, k_begin, k_len, kb0;    // in-sample index of the first row; the sample's keys and first k-block
+  int n_reach, off, n_tiles, count;  // causal-reachable k-blocks, k_len - q_len, K/V tiles to process, active blocks
+};
+static_assert(sizeof(ItemRecord) == kItemWords * 4, "ItemRecord layout");
 
 size_t workspace_bytes(int nhead_k, int num_q_block, int num_k_block, int batch);
 Workspace make_workspace(void* base, int nhead_k, int num_q_block, int num_k_block, int batch);
@@ -41,6 +53,7 @@ struct Problem {
   int num_q_block, num_k_block, qbs, kbs;
   int causal;
   float scale;                          // softmax scale (natural-log domain)
+  int kv_tile;                          // rows of one K/V tile of the tensor-core kernel (0: one tile per k-block)
 };
 
 // Geometry of one (q-block, sample) pair, derived on the device from cu_seqlens only.
@@ -88,8 +101,12 @@ void set_last_error(const char* fmt, ...);
 cudaError_t launch_calculate_blocks(const int32_t* cu_seqlen, int batch, int block_size, int capacity,
                                     int32_t* cu_block, int32_t* block_to_batch, int32_t* cu_num_block,
                                     cudaStream_t stream);
-cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* decisions, bool need_order,
-                            cudaStream_t stream);
+cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* decisions, cudaStream_t stream);
+// Rows of one K/V tile the tensor-core kernel uses for k blocks of `kbs` rows.
+int sm100_kv_tile_rows(int kbs);
+// Debugging aid: clock64 stamps of the first CTA's pipeline events go to this device buffer.
+void sm100_set_trace(long long* device_buffer);
+size_t sm100_trace_bytes();
 cudaError_t launch_forward_generic(const Problem& p, const Workspace& ws, const hbsa_forward_args& a,
                                    cudaStream_t stream);
 // Returns nullptr when eligible, else a static string saying why not.

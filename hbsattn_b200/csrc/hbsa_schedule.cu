@@ -2,10 +2,10 @@
 //
 //  * calculate_blocks_*: the block tables of hbsattn/utils.py:7-50, built by two small kernels
 //    instead of ~12 torch launches.
-//  * schedule_*: from cu_seqlens and the block mask, the number of active k-blocks of every
-//    (kv-head, q-block) row - the exact valid/skip decision - and an ordering of the rows by
-//    descending work so that the attention grid starts with the longest rows (the reference
-//    launches rows in index order, fwd_triton_fix_tile_size.py:242).
+//  * sched_*: from cu_seqlens and the block mask, the number of active k-blocks of every
+//    (kv-head, q-block) row - the exact valid/skip decision - and one ItemRecord per row in the
+//    order the persistent attention kernel drains them (the reference launches one program per
+//    row in index order, fwd_triton_fix_tile_size.py:242).
 #include "hbsa_common.cuh"
 
 namespace hbsa {
@@ -18,8 +18,10 @@ size_t workspace_bytes(int nhead_k, int num_q_block, int /*num_k_block*/, int ba
   b += align_up(kStatusWords * 4, 256);
   b += 2 * align_up((size_t)(batch + 1) * 4, 256);
   b += align_up((size_t)num_q_block * 4, 256);
-  b += 2 * align_up(rows * 4, 256);
-  b += 3 * align_up((size_t)kHistBins * 4, 256);
+  b += align_up(rows * 4, 256);
+  b += align_up(rows * kItemWords * 4, 256);
+  b += align_up(64 * 4, 256);
+  b += align_up((size_t)batch * 4, 256);
   return b;
 }
 
@@ -33,10 +35,9 @@ Workspace make_workspace(void* base, int nhead_k, int num_q_block, int /*num_k_b
   w.cnk = take((size_t)(batch + 1) * 4);
   w.qb2b = take((size_t)num_q_block * 4);
   w.counts = take(rows * 4);
-  w.order = take(rows * 4);
-  w.hist = take((size_t)kHistBins * 4);
-  w.bin_start = take((size_t)kHistBins * 4);
-  w.bin_cursor = take((size_t)kHistBins * 4);
+  w.items = take(rows * kItemWords * 4);
+  w.cursor = take(64 * 4);
+  w.qpos = take((size_t)batch * 4);
   return w;
 }
 
@@ -134,14 +135,28 @@ cudaError_t launch_calculate_blocks(const int32_t* cu_seqlen, int batch, int blo
 // ---------------------------------------------------------------------------------------------
 
 // One CTA: both block-count scans, validation against the mask shape, and clearing of the
-// status word and histogram of this call.
+// status words and the work cursor of this call.
 __global__ void __launch_bounds__(1024) sched_metadata_kernel(Problem p, Workspace ws) {
-  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) { ws.hist[i] = 0; ws.bin_cursor[i] = 0; }
+  if (threadIdx.x < 64) ws.cursor[threadIdx.x] = 0;
   if (threadIdx.x < kStatusWords) ws.status[threadIdx.x] = 0;
   __syncthreads();
   scan_num_blocks(p.cu_q, p.batch, p.qbs, ws.cnq);
   scan_num_blocks(p.cu_k, p.batch, p.kbs, ws.cnk);
   __syncthreads();
+  // Launch position of every sample: samples sorted by descending k_len (ties by index), counted in
+  // q-blocks.  Quadratic in the batch size, so very large batches keep their natural order.
+  for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
+    int pos = ws.cnq[b];
+    if (p.batch <= 4096) {
+      const int len_b = p.cu_k[b + 1] - p.cu_k[b];
+      pos = 0;
+      for (int o = 0; o < p.batch; ++o) {
+        const int len_o = p.cu_k[o + 1] - p.cu_k[o];
+        if (len_o > len_b || (len_o == len_b && o < b)) pos += ws.cnq[o + 1] - ws.cnq[o];
+      }
+    }
+    ws.qpos[b] = pos;
+  }
   if (threadIdx.x == 0) {
     const int nq = ws.cnq[p.batch], nk = ws.cnk[p.batch];
     if (nq != p.num_q_block || nk != p.num_k_block) {
@@ -176,7 +191,24 @@ __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace w
   for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
   if (lane == 0) {
     ws.counts[row] = cnt;
-    atomicAdd(&ws.hist[min(cnt, kHistBins - 1)], 1);
+    int n_tiles = cnt;
+    if (p.kv_tile > 0 && p.kv_tile < p.kbs) {
+      const int n_sub = p.kbs / p.kv_tile;
+      n_tiles = cnt * n_sub;
+      const int j_last = g.nkb - 1;           // the ragged last k-block of the sample may own fewer tiles
+      if (cnt > 0 && j_last < g.n_reach && mrow[(long long)(g.kb0 + j_last) * p.mask_s2] != 0) {
+        const int len_last = g.k_len - j_last * p.kbs;
+        n_tiles -= n_sub - (len_last + p.kv_tile - 1) / p.kv_tile;
+      }
+    }
+    ItemRecord rec;
+    rec.hk = hk; rec.qb = qb; rec.q_begin = g.q_begin; rec.q_end = g.q_end;
+    rec.q_in0 = g.q_in0; rec.k_begin = g.k_begin; rec.k_len = g.k_len; rec.kb0 = g.kb0;
+    rec.n_reach = g.n_reach; rec.off = g.off; rec.n_tiles = n_tiles; rec.count = cnt;
+    // launch position: kv-head, then the sample's slot, q-blocks mirrored (last q-block of the sample first)
+    const int last = ws.cnq[g.b + 1] - 1;
+    const long long pos = (long long)hk * p.num_q_block + (ws.qpos[g.b] + (last - qb));
+    reinterpret_cast<ItemRecord*>(ws.items)[pos] = rec;
   }
   if (decisions) {
     uint8_t* drow = decisions + (size_t)row * p.num_k_block;
@@ -188,35 +220,7 @@ __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace w
   }
 }
 
-// bin_start[c] = number of rows whose bin is larger than c (rows are emitted longest first).
-__global__ void __launch_bounds__(kHistBins) sched_scan_kernel(Workspace ws) {
-  if (ws.status[0] != HBSA_STATUS_OK) return;
-  __shared__ int s[kHistBins];
-  const int t = threadIdx.x;
-  s[t] = ws.hist[kHistBins - 1 - t];       // reversed: index 0 is the largest bin
-  __syncthreads();
-  for (int d = 1; d < kHistBins; d <<= 1) {
-    const int y = t >= d ? s[t - d] : 0;
-    __syncthreads();
-    s[t] += y;
-    __syncthreads();
-  }
-  const int excl = t == 0 ? 0 : s[t - 1];
-  ws.bin_start[kHistBins - 1 - t] = excl;
-}
-
-__global__ void sched_scatter_kernel(Problem p, Workspace ws) {
-  if (ws.status[0] != HBSA_STATUS_OK) return;
-  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long rows = (long long)p.nhead_k * p.num_q_block;
-  if (row >= rows) return;
-  const int bin = min(ws.counts[row], kHistBins - 1);
-  const int pos = atomicAdd(&ws.bin_cursor[bin], 1);
-  ws.order[ws.bin_start[bin] + pos] = (int)row;
-}
-
-cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* decisions, bool need_order,
-                            cudaStream_t stream) {
+cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* decisions, cudaStream_t stream) {
   cudaError_t e;
   sched_metadata_kernel<<<1, 1024, 0, stream>>>(p, ws);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
@@ -225,12 +229,6 @@ cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* deci
   const long long rows = (long long)p.nhead_k * p.num_q_block;
   sched_count_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p, ws, decisions);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  if (need_order) {
-    sched_scan_kernel<<<1, kHistBins, 0, stream>>>(ws);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    sched_scatter_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(p, ws);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  }
   return cudaSuccess;
 }
 

@@ -161,6 +161,12 @@ int hbsa_select_impl(const hbsa_forward_args* args);
  * calls it. */
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
 
+/* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes()
+ * bytes is set, the first CTA of every tensor-core attention launch writes clock64() stamps of its
+ * pipeline events into it (96 tiles x 32 int64 slots).  NULL switches it off (the default). */
+size_t hbsa_debug_trace_bytes(void);
+void hbsa_debug_set_trace(void* device_buffer);
+
 /*
  * hbsa_forward for callers that cannot allocate: identical to hbsa_forward except that the
  * scratch memory is a fixed array inside the library instead of `args->workspace` (which is
@@ -170,7 +176,7 @@ int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
  * cudaMalloc).  The call allocates nothing, on the host side of CUDA or on the device.
  *
  *  - Limit: hbsa_workspace_bytes(nhead_k, num_q_block, num_k_block, batch) must not exceed
- *    HBSA_STATIC_SCRATCH_BYTES (about nhead_k * num_q_block <= 500k rows); larger problems
+ *    HBSA_STATIC_SCRATCH_BYTES (about nhead_k * num_q_block <= 80k rows); larger problems
  *    return HBSA_ERR_WORKSPACE and hbsa_last_error() says how many bytes were needed.
  *  - Cost: every GPU that loads the library carries the array until the process exits.
  *  - The first call on each device looks up the array's device address; make that first call
