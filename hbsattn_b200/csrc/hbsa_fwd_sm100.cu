@@ -17,22 +17,28 @@
 //    double-buffered, so S(t+1) is computed while the softmax warps work on S(t); P (in the input
 //    dtype, as at fwd_triton_fix_tile_size.py:187) is written back into TMEM over the S columns it
 //    came from and consumed as the A operand of the second MMA, so it never touches shared memory.
-//    O is double-buffered across items so that the epilogue of one item overlaps the next.
-//  * Online softmax runs in registers on 256 threads: two threads per row, each owning half of the
-//    tile's columns (row maxima are exchanged through shared memory), exp2 with the scale folded
-//    in; the running output is rescaled only when a row maximum grows by more than 2^8.
+//  * The columns of every tile are split between two softmax warpgroups that never talk to each
+//    other inside an item: group A owns columns [0, ca), group B columns [ca, nt), and each keeps
+//    its own online-softmax state (reference maximum, row sum) and its own output accumulator in
+//    TMEM (O_A, O_B) fed by its own P V products.  The two partial results are merged once per item
+//    in the epilogue, exactly like two key ranges of a split softmax.  Inside a group one thread
+//    owns one row: no shuffles, no shared-memory exchange per tile, and the two warps that share an
+//    SM sub-partition drift out of phase, so one of them keeps the exp unit busy while the other
+//    waits for TMEM.
 //
-// Warp roles (320 threads): warps 0-3 softmax columns [0, ca), warps 4-7 softmax columns [ca, nt)
-// (TMEM lane quarter = warp id % 4), warp 8 work fetch + TMA producer, warp 9 TMEM allocator +
-// MMA issuer.
+// Warp roles (384 threads): warps 0-3 softmax group A, warps 4-7 softmax group B (TMEM lane quarter
+// = warp id % 4), warp 8 work fetch + TMA producer, warp 9 TMEM allocator + issuer of S = Q K^T,
+// warps 10 and 11 issuers of the two groups' P V products.
 //
 // mbarriers.  T counts K/V tiles over the whole life of the CTA, I counts published items, Iq those
 // of them that have tiles.  Two-entry barrier arrays are indexed by the low bit of the count and
 // complete once per use, so a waiter for count c uses entry c & 1 and parity (c >> 1) & 1:
 //   k_full / v_full [T]: TMA bytes landed          s_full [T]: S = Q K^T done (K stage free again)
-//   p_full [T]: P written (one arrival per warp)   pv_done [T]: O += P V done (V stage, S buffer free)
-//   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O out of TMEM
+//   p_full [g][T]: group g wrote its P             pv_done [g][T]: O_g += P_g V done
+//                                                  (both groups done: V stage and S buffer free)
+//   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O_A, O_B out of TMEM
 //   item_full [I]: item slot written               item_done [I]: all consumers left item I
+//   pair [Iq][quarter]: the two threads of a row exchanged (m, l) for the merge
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
@@ -46,10 +52,12 @@ namespace hbsa {
 
 namespace {
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
 constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kTmemCols = 512;       // S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512)
+constexpr int kMmaWarp = 9;          // issues S = Q K^T, owns the TMEM allocation
+constexpr int kPvWarpA = 10;         // issues O_A += P_A V
+constexpr int kPvWarpB = 11;         // issues O_B += P_B V
+constexpr int kTmemCols = 512;       // S0 [0,128)  S1 [128,256)  O_A [256,384)  O_B [384,512)
 constexpr int kTmemOCol = 256;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -59,7 +67,7 @@ struct Sm100Params {
   void* o;
   long long o_s0, o_s1;        // elements
   int nt;                      // rows of one K/V tile (multiple of 16, <= 128)
-  int ca;                      // columns [0, ca) of a tile belong to softmax warps 0-3, [ca, nt) to warps 4-7
+  int ca;                      // columns [0, ca) of a tile belong to softmax group A, [ca, nt) to group B
   int n_sub;                   // K/V tiles per k-block
   int gp, gp_shift;            // q-heads packed into one M tile
   int n_head_sub;              // group / gp
@@ -70,13 +78,14 @@ struct Sm100Params {
   float scale_log2;
   long long wait_budget;       // clock64 ticks
   long long* trace;            // debugging aid: clock64 stamps of CTA 0 (NULL in normal use)
-  int debug;                   // experiments (wrong results!): 1 = softmax does no math, 2 = K/V loaded only for the first tiles
 };
 
 constexpr int kTraceTiles = 96;      // tiles of CTA 0 that are stamped
-constexpr int kTraceSlots = 32;      // stamps per tile (16..23: after every S MMA, 24..31: after every PV MMA)
-// slot meanings: 0 K issued, 1 V issued, 2 MMA warp has K and a free S, 3 QK issued, 4 MMA warp has V and P,
-// 5 PV issued, 6 softmax sees S, 7 row max done, 8 P written, 9 P arrival done, 10 item start (softmax), 11 epilogue done
+constexpr int kTraceSlots = 32;      // stamps per tile
+// slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV_A(t) issue starts, 5 PV_A(t) issued,
+// 6 group A sees S, 7 A: row max done, 8 A: P written, 9 A: P arrival done, 10 item start (A), 11 A: epilogue done,
+// 12 A: S in registers, 14 PV_B(t) issue starts, 15 PV_B(t) issued, 16..21 the same as 6..9,12 for group B (16 sees S,
+// 17 max, 18 P written, 19 arrival, 20 S in registers)
 __device__ __forceinline__ void stamp(long long* trace, int tile, int slot) {
   if (trace != nullptr && blockIdx.x == 0 && tile >= 0 && tile < kTraceTiles) trace[tile * kTraceSlots + slot] = clock64();
 }
@@ -95,17 +104,15 @@ struct ItemSlot {
 
 struct __align__(16) Control {
   unsigned long long item_full[2], item_done[2];
-  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], o_free[2];
+  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], o_free[2];
+  unsigned long long p_full[2][2], pv_done[2][2];      // [group][tile parity]
+  unsigned long long pair[2][4];                       // [item parity][quarter]
   uint32_t tmem_base;
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
-  // Exchange between the two warps that share a TMEM lane quarter (the two threads of a row): values
-  // go through these arrays, hand-over through the pair barriers (count 2, one arrival per warp) -
-  // no thread ever spins on shared memory, which would steal bandwidth from the MMA operand reads.
-  unsigned long long pair_max[2][4], pair_sum[2][4];   // [tile / item parity][quarter]
-  float xmax[2][2][128];                // [tile parity][column half][row]: row maximum of tile T
-  float xsum[2][2][128];                // [item parity][column half][row]: row sum of item Iq
+  float xm[2][2][128];       // [item parity][group][row]: reference maximum at the end of the item
+  float xl[2][2][128];       // [item parity][group][row]: row sum at the end of the item
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -114,42 +121,35 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float h
   else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 
-// P = exp2(S * scale - m) for `N` consecutive columns whose first tile column is c0; columns above
-// col_limit are forced to zero.  Packs pairs to 16 bit and adds to four independent partial sums.
-template <bool BF16, int N>
-__device__ __forceinline__ void softmax_chunk(const uint32_t* r, uint32_t* pk, float scale_log2, float neg_m,
-                                              int c0, int col_limit, float (&sum)[4]) {
-  const bool full = col_limit >= c0 + N - 1;
+// The softmax of one thread works on 16-column groups of its row (one TMEM load / store each), so that
+// a single copy of the code serves every tile width; masked columns are set to -inf beforehand, which
+// exp2 turns into exact zeros.
+__device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
+  mx[0] = max3(mx[0], __uint_as_float(r[0]), __uint_as_float(r[1]));
+  mx[1] = max3(mx[1], __uint_as_float(r[2]), __uint_as_float(r[3]));
+  mx[2] = max3(mx[2], __uint_as_float(r[4]), __uint_as_float(r[5]));
+  mx[3] = max3(mx[3], __uint_as_float(r[6]), __uint_as_float(r[7]));
+  mx[0] = max3(mx[0], __uint_as_float(r[8]), __uint_as_float(r[9]));
+  mx[1] = max3(mx[1], __uint_as_float(r[10]), __uint_as_float(r[11]));
+  mx[2] = max3(mx[2], __uint_as_float(r[12]), __uint_as_float(r[13]));
+  mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
+}
+// P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
+template <bool BF16>
+__device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
 #pragma unroll
-  for (int i = 0; i < N; i += 2) {
-    float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[i]), scale_log2, neg_m));
-    float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m));
-    if (!full) {
-      if (c0 + i > col_limit) p0 = 0.f;
-      if (c0 + i + 1 > col_limit) p1 = 0.f;
-    }
+  for (int i = 0; i < 16; i += 2) {
+    const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[i]), scale_log2, neg_m));
+    const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m));
     sum[(i >> 1) & 1] += p0;
     sum[2 + ((i >> 1) & 1)] += p1;
     pk[i >> 1] = pack2<BF16>(p0, p1);
-  }
-}
-
-// Row maximum over `N` columns into four independent partial maxima.
-template <int N>
-__device__ __forceinline__ void max_chunk(const uint32_t* r, int c0, int col_limit, float (&mx)[4]) {
-  if (col_limit >= c0 + N - 1) {
-#pragma unroll
-    for (int i = 0; i < N; i += 8) {
-      mx[0] = fmaxf(mx[0], fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-      mx[1] = fmaxf(mx[1], fmaxf(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
-      mx[2] = fmaxf(mx[2], fmaxf(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])));
-      mx[3] = fmaxf(mx[3], fmaxf(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < N; ++i)
-      mx[i & 3] = fmaxf(mx[i & 3], (c0 + i <= col_limit) ? __uint_as_float(r[i]) : -INFINITY);
   }
 }
 
@@ -164,36 +164,27 @@ __device__ __forceinline__ uint32_t bar_of(uint32_t base, int c) { return base +
 __device__ __forceinline__ uint32_t par_of(int c) { return (uint32_t)(c >> 1) & 1u; }
 
 // The issue sequences of the MMA thread.  Every descriptor and TMEM address is precomputed into
-// registers once per CTA, so a product is nothing but back-to-back tcgen05.mma instructions: the lone
-// issuing thread needs several clocks per ordinary instruction and would otherwise starve the pipe.
+// registers once per CTA, so a product is nothing but back-to-back tcgen05.mma instructions.
 template <int KSTEPS>
-__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[8], const uint64_t (&kd)[8], uint32_t idesc,
-                                         long long* trace, int T) {
+__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[8], const uint64_t (&kd)[8], uint32_t idesc) {
   ptx::mma_ss_c<false>(tS, qd[0], kd[0], idesc);
-  stamp(trace, T, 16);
 #pragma unroll
-  for (int ks = 1; ks < KSTEPS; ++ks) { ptx::mma_ss_c<true>(tS, qd[ks], kd[ks], idesc); stamp(trace, T, 16 + ks); }
+  for (int ks = 1; ks < KSTEPS; ++ks) ptx::mma_ss_c<true>(tS, qd[ks], kd[ks], idesc);
 }
-template <int KSTEPS>
-__device__ __forceinline__ void issue_pv_steps(uint32_t tO, const uint32_t (&pa)[8], const uint64_t (&vd)[8], uint32_t idesc, bool first,
-                                               long long* trace, int T) {
+// N k-steps of O (+)= P V; the first one overwrites O when `first`.
+template <int N>
+__device__ __forceinline__ void issue_pv_n(uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
   if (first) ptx::mma_ts_c<false>(tO, pa[0], vd[0], idesc);
   else ptx::mma_ts_c<true>(tO, pa[0], vd[0], idesc);
-  stamp(trace, T, 24);
 #pragma unroll
-  for (int ks = 1; ks < KSTEPS; ++ks) { ptx::mma_ts_c<true>(tO, pa[ks], vd[ks], idesc); stamp(trace, T, 24 + ks); }
+  for (int ks = 1; ks < N; ++ks) ptx::mma_ts_c<true>(tO, pa[ks], vd[ks], idesc);
 }
-__device__ __forceinline__ void issue_pv(int ksteps, uint32_t tO, const uint32_t (&pa)[8], const uint64_t (&vd)[8], uint32_t idesc, bool first,
-                                         long long* trace, int T) {
-  switch (ksteps) {
-    case 1: issue_pv_steps<1>(tO, pa, vd, idesc, first, trace, T); break;
-    case 2: issue_pv_steps<2>(tO, pa, vd, idesc, first, trace, T); break;
-    case 3: issue_pv_steps<3>(tO, pa, vd, idesc, first, trace, T); break;
-    case 4: issue_pv_steps<4>(tO, pa, vd, idesc, first, trace, T); break;
-    case 5: issue_pv_steps<5>(tO, pa, vd, idesc, first, trace, T); break;
-    case 6: issue_pv_steps<6>(tO, pa, vd, idesc, first, trace, T); break;
-    case 7: issue_pv_steps<7>(tO, pa, vd, idesc, first, trace, T); break;
-    default: issue_pv_steps<8>(tO, pa, vd, idesc, first, trace, T); break;
+__device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
+  switch (n) {
+    case 1: issue_pv_n<1>(tO, pa, vd, idesc, first); break;
+    case 2: issue_pv_n<2>(tO, pa, vd, idesc, first); break;
+    case 3: issue_pv_n<3>(tO, pa, vd, idesc, first); break;
+    default: issue_pv_n<4>(tO, pa, vd, idesc, first); break;
   }
 }
 
@@ -212,6 +203,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(P.o);
+  const bool has_b = P.nt > P.ca;                  // group B owns at least one 16-column step
 
   // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle)
   extern __shared__ uint8_t smem_raw[];
@@ -225,8 +217,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t bar_item_full = smem_u32(&ctl->item_full[0]), bar_item_done = smem_u32(&ctl->item_done[0]);
   const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
   const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
-  const uint32_t bar_p_full = smem_u32(&ctl->p_full[0]), bar_pv_done = smem_u32(&ctl->pv_done[0]);
   const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]);
+  const uint32_t bar_p_full_a = smem_u32(&ctl->p_full[0][0]), bar_p_full_b = smem_u32(&ctl->p_full[1][0]);
+  const uint32_t bar_pv_done_a = smem_u32(&ctl->pv_done[0][0]), bar_pv_done_b = smem_u32(&ctl->pv_done[1][0]);
   volatile int* const abort_flag = &ctl->abort_flag;
   volatile int* const tile_k0 = ctl->tile_k0;
   volatile ItemSlot* const slots = ctl->slot;
@@ -234,23 +227,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_item_full + 8 * i, 1);
-      mbar_init(bar_item_done + 8 * i, 9);      // 8 softmax warps + the MMA warp
+      mbar_init(bar_item_done + 8 * i, 11);     // 8 softmax warps + the three MMA issuing threads
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_k_full + 8 * i, 1);
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_p_full + 8 * i, 8);
-      mbar_init(bar_pv_done + 8 * i, 1);
       mbar_init(bar_o_free + 8 * i, 8);
-      for (int qd = 0; qd < 4; ++qd) {
-        mbar_init(smem_u32(&ctl->pair_max[i][qd]), 2);
-        mbar_init(smem_u32(&ctl->pair_sum[i][qd]), 2);
-      }
+      mbar_init(bar_p_full_a + 8 * i, 4);
+      mbar_init(bar_p_full_b + 8 * i, 4);
+      mbar_init(bar_pv_done_a + 8 * i, 1);
+      mbar_init(bar_pv_done_b + 8 * i, 1);
+      for (int qd = 0; qd < 4; ++qd) mbar_init(smem_u32(&ctl->pair[i][qd]), 2);
     }
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
-
   if (warp == kProducerWarp && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
@@ -346,21 +337,23 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (lane == 0) {
               tile_k0[T & 3] = k0;
               __threadfence_block();
-              if ((P.debug & 2) && T >= 2) mbar_arrive(bar_of(bar_k_full, T));
-              else mbar_arrive_expect_tx(bar_of(bar_k_full, T), kv_tile_bytes);
+              mbar_arrive_expect_tx(bar_of(bar_k_full, T), kv_tile_bytes);
 #pragma unroll
               for (int pn = 0; pn < PANELS; ++pn)
-                if (!((P.debug & 2) && T >= 2)) tma_load_3d(sK + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_k, bar_of(bar_k_full, T), pn * 64, rec.hk, rec.k_begin + k0);
+                tma_load_3d(sK + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_k, bar_of(bar_k_full, T), pn * 64, rec.hk, rec.k_begin + k0);
               stamp(P.trace, T, 0);
             }
-            if (T >= 2) ok = warp_wait(bar_of(bar_pv_done, T), par_of(T - 2), abort_flag, budget);
+            // V stage T & 1 is free once both groups' P V products of tile T-2 are done
+            if (T >= 2) {
+              ok = warp_wait(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
+              if (ok && has_b) ok = warp_wait(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
+            }
             if (!ok) break;
             if (lane == 0) {
-              if ((P.debug & 2) && T >= 2) mbar_arrive(bar_of(bar_v_full, T));
-              else mbar_arrive_expect_tx(bar_of(bar_v_full, T), kv_tile_bytes);
+              mbar_arrive_expect_tx(bar_of(bar_v_full, T), kv_tile_bytes);
 #pragma unroll
               for (int pn = 0; pn < PANELS; ++pn)
-                if (!((P.debug & 2) && T >= 2)) tma_load_3d(sV + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_v, bar_of(bar_v_full, T), pn * 64, rec.hk, rec.k_begin + k0);
+                tma_load_3d(sV + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_v, bar_of(bar_v_full, T), pn * 64, rec.hk, rec.k_begin + k0);
               stamp(P.trace, T, 1);
             }
             ++T;
@@ -376,24 +369,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
   } else if (warp == kMmaWarp) {
-    // =============================== MMA issuer ===============================
-    // One thread runs an event loop: whichever of "the oldest P V product whose P is written" and "the
-    // next S = Q K^T whose K tile has landed and whose S buffer is free" is ready gets issued, so the
-    // tensor pipe works on S(t+1) while the softmax warps are busy with S(t) and P V(t) starts the
-    // moment P(t) exists.  All probes are non-blocking; a clock budget bounds the loop.
+    // =============================== issuer of S = Q K^T ===============================
+    // tcgen05.mma costs the lone issuing thread ~50 clocks apiece (more when its SM sub-partition is
+    // busy), about what the tensor pipe needs to execute one, so the three kinds of products are
+    // issued by three threads on three sub-partitions, each blocking on exactly its own barriers.
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(BF16, false, false, 128, P.nt);
-      const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
-      const int ksteps_pv = P.nt >> 4;
-      const int ca_steps = P.ca >> 4;
-      const uint32_t p_jump = (uint32_t)P.ca >> 1;                 // P of columns [ca, nt) starts at S + ca
       const uint32_t desc_hi = smem_desc_hi(1024u);
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
       // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
-      // V is MN-major: 16 keys further = 2048 bytes = 128 units.  P: 8 TMEM columns per 16 keys, columns
-      // [0, ca) at S + 0.., columns [ca, nt) at S + ca..
-      uint64_t qd0[8], qd1[8], kd0[8], kd1[8], vd0[8], vd1[8];
-      uint32_t pa0[8], pa1[8];
+      uint64_t qd0[8], qd1[8], kd0[8], kd1[8];
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
@@ -402,102 +387,117 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         qd1[ks] = smem_desc_join(smem_desc_lo(sQ + Q_BYTES, 16u) + qo, desc_hi);
         kd0[ks] = smem_desc_join(smem_desc_lo(sK, 16u) + ko, desc_hi);
         kd1[ks] = smem_desc_join(smem_desc_lo(sK + KV_BYTES_MAX, 16u) + ko, desc_hi);
-        vd0[ks] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
-        vd1[ks] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
-        const uint32_t po = (uint32_t)ks * 8u + (ks >= ca_steps ? p_jump : 0u);
-        pa0[ks] = tmem_base + po;
-        pa1[ks] = tmem_base + 128u + po;
       }
       int I = 0, Iq = 0, T = 0;
-      bool have_item = false, finished = false, first = false;
-      int n_left = 0;
-      // P V products that have their S issued but are not issued themselves (at most two: T-2 is done
-      // before S(T) may start), oldest first
-      int pv_T[2] = {-1, -1}, pv_first[2] = {0, 0}, pv_iq[2] = {0, 0}, pv_n = 0;
-      long long t_progress = clock64();
-      while (true) {
-        bool progress = false;
-        if (!have_item && !finished && mbar_test(bar_of(bar_item_full, I), par_of(I))) {
-          const int n_tiles = slots[I & 1].n_tiles;
-          if (n_tiles < 0) {
-            finished = true;
-          } else if (n_tiles == 0) {
-            mbar_arrive(bar_of(bar_item_done, I));
-            ++I;
-          } else {
-            have_item = true;
-            first = true;
-            n_left = n_tiles;
-          }
-          progress = true;
-        }
-        if (pv_n > 0) {
-          const int pT = pv_T[0];
-          bool ready = mbar_test(bar_of(bar_p_full, pT), par_of(pT)) && mbar_test(bar_of(bar_v_full, pT), par_of(pT));
-          // the first P V of an item overwrites O: the epilogue of the item two before must have read it
-          if (ready && pv_first[0] && pv_iq[0] >= 2) ready = mbar_test(bar_of(bar_o_free, pv_iq[0]), par_of(pv_iq[0] - 2));
-          if (ready) {
-            tc_fence_after();
-            stamp(P.trace, pT, 4);
-            const uint32_t tOb = tmem_base + kTmemOCol + (uint32_t)(pv_iq[0] & 1) * 128u;
-            if (pT & 1) issue_pv(ksteps_pv, tOb, pa1, vd1, idesc_pv, pv_first[0] != 0, P.trace, pT);
-            else issue_pv(ksteps_pv, tOb, pa0, vd0, idesc_pv, pv_first[0] != 0, P.trace, pT);
-            tc_commit(bar_of(bar_pv_done, pT));
-            stamp(P.trace, pT, 5);
-            pv_T[0] = pv_T[1]; pv_first[0] = pv_first[1]; pv_iq[0] = pv_iq[1];
-            --pv_n;
-            progress = true;
-          }
-        }
-        if (have_item && pv_n < 2) {
-          bool ready = mbar_test(bar_of(bar_k_full, T), par_of(T));
-          if (ready && first) ready = mbar_test(bar_of(bar_q_full, Iq), par_of(Iq));
-          // S buffer T & 1 held P(T-2): free once PV(T-2) is done
-          if (ready && T >= 2) ready = mbar_test(bar_of(bar_pv_done, T), par_of(T - 2));
-          if (ready) {
+      bool ok = true;
+      while (ok) {
+        ok = mbar_wait_bounded(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
+        if (!ok) break;
+        const int n_tiles = slots[I & 1].n_tiles;
+        if (n_tiles < 0) break;
+        if (n_tiles > 0) {
+          ok = mbar_wait_bounded(bar_of(bar_q_full, Iq), par_of(Iq), abort_flag, budget);
+          for (int t = 0; t < n_tiles && ok; ++t, ++T) {
+            ok = mbar_wait_bounded(bar_of(bar_k_full, T), par_of(T), abort_flag, budget);
+            // S buffer T & 1 held P(T-2): free once both groups' P V products of tile T-2 are done
+            if (ok && T >= 2) {
+              ok = mbar_wait_bounded(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
+              if (ok && has_b) ok = mbar_wait_bounded(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
+            }
+            if (!ok) break;
             tc_fence_after();
             stamp(P.trace, T, 2);
             const uint32_t tSb = tmem_base + (uint32_t)(T & 1) * 128u;
             if (Iq & 1) {
-              if (T & 1) issue_qk<D / 16>(tSb, qd1, kd1, idesc_qk, P.trace, T);
-              else issue_qk<D / 16>(tSb, qd1, kd0, idesc_qk, P.trace, T);
+              if (T & 1) issue_qk<D / 16>(tSb, qd1, kd1, idesc_qk);
+              else issue_qk<D / 16>(tSb, qd1, kd0, idesc_qk);
             } else {
-              if (T & 1) issue_qk<D / 16>(tSb, qd0, kd1, idesc_qk, P.trace, T);
-              else issue_qk<D / 16>(tSb, qd0, kd0, idesc_qk, P.trace, T);
+              if (T & 1) issue_qk<D / 16>(tSb, qd0, kd1, idesc_qk);
+              else issue_qk<D / 16>(tSb, qd0, kd0, idesc_qk);
             }
             tc_commit(bar_of(bar_s_full, T));
             stamp(P.trace, T, 3);
-            pv_T[pv_n] = T; pv_first[pv_n] = first ? 1 : 0; pv_iq[pv_n] = Iq;
-            ++pv_n;
-            ++T;
-            first = false;
-            if (--n_left == 0) {
-              mbar_arrive(bar_of(bar_item_done, I));
-              ++I;
-              ++Iq;
-              have_item = false;
-            }
-            progress = true;
           }
+          ++Iq;
         }
-        if (finished && pv_n == 0) break;
-        if (progress) {
-          t_progress = clock64();
-        } else {
-          if (*abort_flag) break;
-          if (clock64() - t_progress > budget) { *abort_flag = 1; break; }
+        if (!ok) break;
+        mbar_arrive(bar_of(bar_item_done, I));
+        ++I;
+      }
+    }
+    __syncwarp();
+  } else if (warp == kPvWarpA || warp == kPvWarpB) {
+    // =============================== issuers of O_g += P_g V ===============================
+    if (lane == 0) {
+      const int g = warp == kPvWarpA ? 0 : 1;
+      const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
+      const uint32_t desc_hi = smem_desc_hi(1024u);
+      const int ca_steps = P.ca >> 4;
+      const int k_first = g == 0 ? 0 : ca_steps;                     // this group's 16-key steps of a tile
+      const int n_steps = g == 0 ? ca_steps : (P.nt >> 4) - ca_steps;
+      const uint32_t bar_p_full = g == 0 ? bar_p_full_a : bar_p_full_b;
+      const uint32_t bar_pv_done = g == 0 ? bar_pv_done_a : bar_pv_done_b;
+      const uint32_t tOg = tmem_base + kTmemOCol + (uint32_t)g * 128u;
+      // V is MN-major: 16 keys further = 2048 bytes = 128 descriptor units.  P: 8 TMEM columns per 16 keys,
+      // group A's at S + 0.., group B's at S + ca..
+      uint64_t vd0[4], vd1[4];
+      uint32_t pa0[4], pa1[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t ks = (uint32_t)(k_first + i);
+        vd0[i] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + ks * 128u, desc_hi);
+        vd1[i] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + ks * 128u, desc_hi);
+        const uint32_t po = (g == 0 ? 0u : (uint32_t)P.ca) + (uint32_t)i * 8u;
+        pa0[i] = tmem_base + po;
+        pa1[i] = tmem_base + 128u + po;
+      }
+      int I = 0, Iq = 0, T = 0;
+      bool ok = true;
+      while (ok) {
+        ok = mbar_wait_bounded(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
+        if (!ok) break;
+        const int n_tiles = slots[I & 1].n_tiles;
+        if (n_tiles < 0) break;
+        if (n_tiles > 0) {
+          if (n_steps > 0) {
+            for (int t = 0; t < n_tiles && ok; ++t, ++T) {
+              ok = mbar_wait_bounded(bar_of(bar_v_full, T), par_of(T), abort_flag, budget);
+              if (ok) ok = mbar_wait_bounded(bar_of(bar_p_full, T), par_of(T), abort_flag, budget);
+              // the first P V of an item overwrites O: the epilogue of the previous item must have read it
+              if (ok && t == 0 && Iq >= 1) ok = mbar_wait_bounded(bar_of(bar_o_free, Iq - 1), par_of(Iq - 1), abort_flag, budget);
+              if (!ok) break;
+              tc_fence_after();
+              stamp(P.trace, T, g == 0 ? 4 : 14);
+              if (T & 1) issue_pv(n_steps, tOg, pa1, vd1, idesc_pv, t == 0);
+              else issue_pv(n_steps, tOg, pa0, vd0, idesc_pv, t == 0);
+              tc_commit(bar_of(bar_pv_done, T));
+              stamp(P.trace, T, g == 0 ? 5 : 15);
+            }
+          } else {
+            T += n_tiles;
+          }
+          ++Iq;
         }
+        if (!ok) break;
+        mbar_arrive(bar_of(bar_item_done, I));
+        ++I;
       }
     }
     __syncwarp();
   } else {
     // =============================== softmax + epilogue ===============================
-    const int half = tid >> 7;                       // 0: columns [0, ca), 1: columns [ca, nt)
+    const int grp = tid >> 7;                        // 0: group A, columns [0, ca); 1: group B, columns [ca, nt)
     const int row = tid & 127;
     const int quarter = warp & 3;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const int my_c0 = half == 0 ? 0 : P.ca;          // first tile column of this thread
-    const int my_nc = half == 0 ? P.ca : P.nt - P.ca; // columns of this thread: 0, 16, 32, 48 or 64
+    const int my_c0 = grp == 0 ? 0 : P.ca;           // first tile column of this thread
+    const int my_nc = grp == 0 ? P.ca : P.nt - P.ca; // columns of this thread: 0, 16, 32, 48 or 64
+    const bool active = my_nc > 0;
+    const uint32_t bar_p_full = grp == 0 ? bar_p_full_a : bar_p_full_b;
+    const uint32_t bar_pv_done = grp == 0 ? bar_pv_done_a : bar_pv_done_b;
+    const uint32_t tOmine = tmem_base + kTmemOCol + (uint32_t)grp * 128u + lane_off;   // this group's accumulator
+    const uint32_t tOa = tmem_base + kTmemOCol + lane_off, tOb = tOa + 128u;
+    const int so = grp * 6 + (grp ? 4 : 0);          // trace slot offset: group A 6.., group B 16..
     const float scale_log2 = P.scale_log2;
     int I = 0, Iq = 0, T = 0;
     bool ok = true;
@@ -510,7 +510,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int r_head = slots[I & 1].head0 + (row & (P.gp - 1));
       const bool r_valid = r_tok < slots[I & 1].q_end;
       // each of the two threads of a row stores half of the head dimension
-      OutT* const orow = o_base + r_tok * P.o_s0 + r_head * P.o_s1 + half * (D / 2);
+      OutT* const orow = o_base + r_tok * P.o_s0 + r_head * P.o_s1 + grp * (D / 2);
       if (n_tiles == 0) {
         // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
         if (r_valid) {
@@ -519,147 +519,143 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
         }
       } else {
-        const uint32_t tO = tmem_base + kTmemOCol + (uint32_t)(Iq & 1) * 128u + lane_off;
         int limit_row = slots[I & 1].k_len - 1;
         if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
         if (tid == 0) stamp(P.trace, T, 10);
-        for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-          ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
-          if (!ok) break;
-          tc_fence_after();
-          if (tid == 0) stamp(P.trace, T, 6);
-          const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
-          const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * 128u + lane_off + (uint32_t)my_c0;
+        if (active) {
+          for (int t = 0; t < n_tiles && ok; ++t, ++T) {
+            ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0 && quarter == 0) stamp(P.trace, T, 6 + so);
+            const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
+            const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * 128u + lane_off + (uint32_t)my_c0;
 
-          // ---- this thread's columns of S, all in registers
-          uint32_t r[64];
-          if (my_nc >= 32) tmem_ld32(tSmine, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-          if (my_nc >= 64) tmem_ld32(tSmine + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-          if (my_nc == 16) tmem_ld16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-          if (my_nc == 48) tmem_ld16(tSmine + 32, *reinterpret_cast<uint32_t(*)[16]>(&r[32]));
-          tmem_wait_ld();
-          if (tid == 0) stamp(P.trace, T, 12);
-          if (P.debug & 1) {
-            if (my_nc >= 32) tmem_st16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-            if (my_nc >= 64) tmem_st16(tSmine + 16, *reinterpret_cast<uint32_t(*)[16]>(&r[32]));
+            // ---- this thread's columns of S, all in registers
+            uint32_t r[64];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
+            tmem_wait_ld();
+            if (lane == 0 && quarter == 0) stamp(P.trace, T, 12 + (grp ? 8 : 0));
+            if (col_limit < my_c0 + my_nc - 1) {
+              // tile on the causal diagonal or at the ragged end of the sample: mask in place
+#pragma unroll
+              for (int i = 0; i < 64; ++i)
+                if (my_c0 + i > col_limit) r[i] = 0xff800000u;             // -inf
+            }
+
+            // ---- row maximum over this group's columns only
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (my_nc > 16 * j) max16(&r[16 * j], mx4);
+            const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
+            if (lane == 0 && quarter == 0) stamp(P.trace, T, 7 + so);
+            if (t == 0) {
+              m_ref = mx_s;
+            } else {
+              const bool need = mx_s > m_ref + kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {
+                // this group's O and l move to the new reference maximum; needs its P V of the previous tile
+                ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+                if (!ok) break;
+                tc_fence_after();
+                const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                  uint32_t o[32];
+                  tmem_ld32(tOmine + c0, o);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                  tmem_st32(tOmine + c0, o);
+                }
+                tmem_wait_st();
+                l *= alpha;
+                if (need) m_ref = mx_s;
+              }
+            }
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+
+            // ---- P = exp2(S * scale - m) packed to 16 bit over this thread's own S columns, row sum
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (my_nc > 16 * j) {
+                uint32_t pk[8];
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+                tmem_st8(tSmine + 8 * j, pk);
+              }
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tmem_wait_st();
             tc_fence_before();
+            if (lane == 0 && quarter == 0) stamp(P.trace, T, 8 + so);
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));
-            if (tid == 0) stamp(P.trace, T, 9);
-            continue;
+            if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
+            if (lane == 0 && quarter == 0) stamp(P.trace, T, 9 + so);
           }
-
-          // ---- row maximum: own columns, then the other half's through shared memory
-          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-          if (my_nc >= 32) max_chunk<32>(&r[0], my_c0, col_limit, mx4);
-          if (my_nc >= 64) max_chunk<32>(&r[32], my_c0 + 32, col_limit, mx4);
-          if (my_nc == 16) max_chunk<16>(&r[0], my_c0, col_limit, mx4);
-          if (my_nc == 48) max_chunk<16>(&r[32], my_c0 + 32, col_limit, mx4);
-          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-          if (tid == 0) stamp(P.trace, T, 13);
-          {
-            ctl->xmax[T & 1][half][row] = mx;
-            __syncwarp();
-            const uint32_t pb = smem_u32(&ctl->pair_max[T & 1][quarter]);
-            if (lane == 0) mbar_arrive(pb);
-            ok = warp_wait(pb, par_of(T), abort_flag, budget);
-            if (!ok) break;
-            mx = fmaxf(mx, *reinterpret_cast<volatile float*>(&ctl->xmax[T & 1][half ^ 1][row]));
-          }
-          if (tid == 0) stamp(P.trace, T, 7);
-          const float mx_s = mx * scale_log2;                          // scale > 0 keeps the order
-          if (t == 0) {
-            m_ref = mx_s;
-          } else {
-            const bool need = mx_s > m_ref + kRescaleThreshold;
-            if (__any_sync(0xffffffffu, need)) {
-              // O and l move to the new reference maximum; needs O += P V of the previous tile.
-              // Both warps of a row pair take this branch together (same maxima) and split O's columns.
-              ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
-              if (!ok) break;
-              tc_fence_after();
-              const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
-#pragma unroll
-              for (int c0 = 0; c0 < D / 2; c0 += 32) {
-                uint32_t o[32];
-                tmem_ld32(tO + half * (D / 2) + c0, o);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                tmem_st32(tO + half * (D / 2) + c0, o);
-              }
-              tmem_wait_st();
-              l *= alpha;
-              if (need) m_ref = mx_s;
-            }
-          }
-          const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-
-          // ---- P = exp2(S * scale - m) packed to 16 bit over this thread's own S columns, row sum
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
-          uint32_t pk[32];
-          if (my_nc >= 32) {
-            softmax_chunk<BF16, 32>(&r[0], &pk[0], scale_log2, neg_m, my_c0, col_limit, sum);
-            tmem_st16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
-          }
-          if (my_nc >= 64) {
-            softmax_chunk<BF16, 32>(&r[32], &pk[16], scale_log2, neg_m, my_c0 + 32, col_limit, sum);
-            tmem_st16(tSmine + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
-          }
-          if (my_nc == 16) {
-            softmax_chunk<BF16, 16>(&r[0], &pk[0], scale_log2, neg_m, my_c0, col_limit, sum);
-            tmem_st8(tSmine, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
-          }
-          if (my_nc == 48) {
-            softmax_chunk<BF16, 16>(&r[32], &pk[16], scale_log2, neg_m, my_c0 + 32, col_limit, sum);
-            tmem_st8(tSmine + 16, *reinterpret_cast<uint32_t(*)[8]>(&pk[16]));
-          }
-          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-          tmem_wait_st();
-          tc_fence_before();
-          if (tid == 0) stamp(P.trace, T, 8);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
-          if (tid == 0) stamp(P.trace, T, 9);
+          if (!ok) break;
+        } else {
+          T += n_tiles;                              // group B without columns (16-row K/V tiles): nothing per tile
         }
-        if (!ok) break;
 
-        // ---- epilogue: the row sum is the sum of both halves; O / l -> global with 16-byte stores,
-        //      rows past the q-block end are dropped
+        // ---- merge of the two groups: (m, l) of both, O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)),
+        //      each thread of a row pair produces half of the head dimension; 16-byte stores, rows past the
+        //      q-block end are dropped
+        ctl->xm[Iq & 1][grp][row] = m_ref;
+        ctl->xl[Iq & 1][grp][row] = l;
+        __syncwarp();
         {
-          ctl->xsum[Iq & 1][half][row] = l;
-          __syncwarp();
-          const uint32_t pb = smem_u32(&ctl->pair_sum[Iq & 1][quarter]);
+          const uint32_t pb = smem_u32(&ctl->pair[Iq & 1][quarter]);
           if (lane == 0) mbar_arrive(pb);
           ok = warp_wait(pb, par_of(Iq), abort_flag, budget);
           if (!ok) break;
-          l += *reinterpret_cast<volatile float*>(&ctl->xsum[Iq & 1][half ^ 1][row]);
         }
-        ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+        const float m_o = *reinterpret_cast<volatile float*>(&ctl->xm[Iq & 1][grp ^ 1][row]);
+        const float l_o = *reinterpret_cast<volatile float*>(&ctl->xl[Iq & 1][grp ^ 1][row]);
+        const float m_a = grp == 0 ? m_ref : m_o, m_b = grp == 0 ? m_o : m_ref;
+        const float l_a = grp == 0 ? l : l_o, l_b = grp == 0 ? l_o : l;
+        const float m_all = fmaxf(m_a, m_b);
+        const float w_a = m_a == -INFINITY ? 0.f : ex2_approx(m_a - m_all);
+        const float w_b = (!has_b || m_b == -INFINITY) ? 0.f : ex2_approx(m_b - m_all);
+        const float denom = l_a * w_a + l_b * w_b;
+        const bool live = denom > 0.f;                                      // rows that saw no key are exact zeros
+        const float f_a = live ? w_a / denom : 0.f, f_b = live ? w_b / denom : 0.f;
+        ok = warp_wait(bar_of(bar_pv_done_a, T - 1), par_of(T - 1), abort_flag, budget);
+        if (ok && has_b) ok = warp_wait(bar_of(bar_pv_done_b, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        uint32_t oa[32], ob[32];
-        tmem_ld32(tO + half * (D / 2), oa);
-        if (D == 128) tmem_ld32(tO + half * (D / 2) + 32, ob);
-        tmem_wait_ld();
-        tc_fence_before();                                               // O is in registers: the buffer may be overwritten
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
-        if (r_valid) {
-          uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-          for (int i = 0; i < D / 16; ++i) {
-            const uint32_t* rr = i < 4 ? oa : ob;
-            const int b = (i & 3) * 8;
-            uint32_t w0 = pack2<BF16>(__uint_as_float(rr[b]) * inv, __uint_as_float(rr[b + 1]) * inv);
-            uint32_t w1 = pack2<BF16>(__uint_as_float(rr[b + 2]) * inv, __uint_as_float(rr[b + 3]) * inv);
-            uint32_t w2 = pack2<BF16>(__uint_as_float(rr[b + 4]) * inv, __uint_as_float(rr[b + 5]) * inv);
-            uint32_t w3 = pack2<BF16>(__uint_as_float(rr[b + 6]) * inv, __uint_as_float(rr[b + 7]) * inv);
-            if (!(l > 0.f)) w0 = w1 = w2 = w3 = 0u;      // rows that saw no key are exact zeros
-            dst[i] = make_uint4(w0, w1, w2, w3);
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          uint32_t oa[32], ob[32];
+          tmem_ld32(tOa + grp * (D / 2) + c0, oa);
+          if (has_b) tmem_ld32(tOb + grp * (D / 2) + c0, ob);
+          tmem_wait_ld();
+          if (c0 + 32 >= D / 2) {
+            tc_fence_before();                                             // both accumulators are in registers
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
+          }
+          if (r_valid) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int e = i * 8 + j * 2;
+                float x0 = __uint_as_float(oa[e]) * f_a, x1 = __uint_as_float(oa[e + 1]) * f_a;
+                if (has_b) {
+                  x0 = fmaf(__uint_as_float(ob[e]), f_b, x0);
+                  x1 = fmaf(__uint_as_float(ob[e + 1]), f_b, x1);
+                }
+                w[j] = live ? pack2<BF16>(x0, x1) : 0u;
+              }
+              dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
           }
         }
         ++Iq;
@@ -785,7 +781,6 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.scale_log2 = p.scale * 1.4426950408889634f;
   P.wait_budget = 4000000000ll;
   P.trace = g_trace;
-  { const char* dbg = getenv("HBSA_DEBUG"); P.debug = dbg ? atoi(dbg) : 0; }
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
   if (P.total_items <= 0) { *err_text = "no work items"; return HBSA_ERR_SHAPE; }
