@@ -111,6 +111,7 @@ struct __align__(16) Control {
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
+  uint4 stage[8][32][4];     // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
   float xm[2][2][128];       // [item parity][group][row]: reference maximum at the end of the item
   float xl[2][2][128];       // [item parity][group][row]: row sum at the end of the item
 };
@@ -186,6 +187,108 @@ __device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa
     case 3: issue_pv_n<3>(tO, pa, vd, idesc, first); break;
     default: issue_pv_n<4>(tO, pa, vd, idesc, first); break;
   }
+}
+
+// Arguments of the deferred merge + store of one work item (see softmax_epilogue).
+struct EpilogueArgs {
+  Control* ctl;
+  void* o;
+  long long o_s0, o_s1, budget;
+  long long* trace;
+  volatile int* abort_flag;
+  uint32_t tOa, tOb, bar_pv_done_a, bar_pv_done_b, bar_o_free;
+  int gp, gp_shift, grp, has_b;
+  float m, l;                 // this thread's reference maximum and row sum at the end of the item
+  int iq, tlast, tok0, head0, qend;
+};
+
+// Merge of the two softmax groups and store of one work item: with (m, l) of both groups,
+// O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)); each thread of a row pair produces half
+// of the head dimension.  Kept out of line: it runs once per item from several places of the tile loop.
+template <int D, bool BF16>
+__device__ __noinline__ bool softmax_epilogue(const EpilogueArgs a) {
+  using namespace ptx;
+  using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+  OutT* const o_base = static_cast<OutT*>(a.o);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = tid & 127, quarter = warp & 3;
+  bool ok = true;
+        a.ctl->xm[a.iq & 1][a.grp][row] = a.m;
+        a.ctl->xl[a.iq & 1][a.grp][row] = a.l;
+        __syncwarp();
+        {
+          const uint32_t pb = smem_u32(&a.ctl->pair[a.iq & 1][quarter]);
+          if (lane == 0) mbar_arrive(pb);
+          ok = warp_wait(pb, par_of(a.iq), a.abort_flag, a.budget);
+          if (!ok) return false;
+        }
+        if (tid == 0) stamp(a.trace, a.tlast, 13);
+        const float m_o = *reinterpret_cast<volatile float*>(&a.ctl->xm[a.iq & 1][a.grp ^ 1][row]);
+        const float l_o = *reinterpret_cast<volatile float*>(&a.ctl->xl[a.iq & 1][a.grp ^ 1][row]);
+        const float m_a = a.grp == 0 ? a.m : m_o, m_b = a.grp == 0 ? m_o : a.m;
+        const float l_a = a.grp == 0 ? a.l : l_o, l_b = a.grp == 0 ? l_o : a.l;
+        const float m_all = fmaxf(m_a, m_b);
+        const float w_a = m_a == -INFINITY ? 0.f : ex2_approx(m_a - m_all);
+        const float w_b = (!a.has_b || m_b == -INFINITY) ? 0.f : ex2_approx(m_b - m_all);
+        const float denom = l_a * w_a + l_b * w_b;
+        const bool live = denom > 0.f;                                      // rows that saw no key are exact zeros
+        const float f_a = live ? w_a / denom : 0.f, f_b = live ? w_b / denom : 0.f;
+        ok = warp_wait(bar_of(a.bar_pv_done_a, a.tlast), par_of(a.tlast), a.abort_flag, a.budget);
+        if (ok && a.has_b) ok = warp_wait(bar_of(a.bar_pv_done_b, a.tlast), par_of(a.tlast), a.abort_flag, a.budget);
+        if (!ok) return false;
+        tc_fence_after();
+        if (tid == 0) stamp(a.trace, a.tlast, 22);
+        const int tile_tok0 = a.tok0, head0 = a.head0, q_end = a.qend;
+#pragma unroll
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+          uint32_t oa[32], ob[32];
+          tmem_ld32(a.tOa + a.grp * (D / 2) + c0, oa);
+          if (a.has_b) tmem_ld32(a.tOb + a.grp * (D / 2) + c0, ob);
+          tmem_wait_ld();
+          if (c0 + 32 >= D / 2) {
+            tc_fence_before();                                             // both accumulators are in registers
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_of(a.bar_o_free, a.iq));
+            if (tid == 0) stamp(a.trace, a.tlast, 23);
+          }
+          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
+          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
+          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
+          uint4* const st = &a.ctl->stage[warp][0][0];
+          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 24);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int e = i * 8 + j * 2;
+              float x0 = __uint_as_float(oa[e]) * f_a, x1 = __uint_as_float(oa[e + 1]) * f_a;
+              if (a.has_b) {
+                x0 = fmaf(__uint_as_float(ob[e]), f_b, x0);
+                x1 = fmaf(__uint_as_float(ob[e + 1]), f_b, x1);
+              }
+              w[j] = live ? pack2<BF16>(x0, x1) : 0u;
+            }
+            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          __syncwarp();
+          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 25);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
+            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
+            const int rg = quarter * 32 + rr;                               // row of the M tile
+            const int tok = tile_tok0 + (rg >> a.gp_shift);
+            if (tok < q_end) {
+              OutT* dst = o_base + tok * a.o_s0 + (head0 + (rg & (a.gp - 1))) * a.o_s1 + a.grp * (D / 2) + c0 + cc * 8;
+              *reinterpret_cast<uint4*>(dst) = val;
+            }
+          }
+          __syncwarp();
+          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 26);
+        }
+  if (tid == 0) stamp(a.trace, a.tlast, 11);
+  return true;
 }
 
 template <int D, bool BF16>
@@ -398,11 +501,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (n_tiles > 0) {
           ok = mbar_wait_bounded(bar_of(bar_q_full, Iq), par_of(Iq), abort_flag, budget);
           for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-            ok = mbar_wait_bounded(bar_of(bar_k_full, T), par_of(T), abort_flag, budget);
+            ok = mbar_spin_bounded(bar_of(bar_k_full, T), par_of(T), abort_flag, budget);
             // S buffer T & 1 held P(T-2): free once both groups' P V products of tile T-2 are done
             if (ok && T >= 2) {
-              ok = mbar_wait_bounded(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
-              if (ok && has_b) ok = mbar_wait_bounded(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
+              ok = mbar_spin_bounded(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
+              if (ok && has_b) ok = mbar_spin_bounded(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
             }
             if (!ok) break;
             tc_fence_after();
@@ -461,8 +564,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (n_tiles > 0) {
           if (n_steps > 0) {
             for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-              ok = mbar_wait_bounded(bar_of(bar_v_full, T), par_of(T), abort_flag, budget);
-              if (ok) ok = mbar_wait_bounded(bar_of(bar_p_full, T), par_of(T), abort_flag, budget);
+              ok = mbar_spin_bounded(bar_of(bar_v_full, T), par_of(T), abort_flag, budget);
+              if (ok) ok = mbar_spin_bounded(bar_of(bar_p_full, T), par_of(T), abort_flag, budget);
               // the first P V of an item overwrites O: the epilogue of the previous item must have read it
               if (ok && t == 0 && Iq >= 1) ok = mbar_wait_bounded(bar_of(bar_o_free, Iq - 1), par_of(Iq - 1), abort_flag, budget);
               if (!ok) break;
@@ -501,24 +604,37 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float scale_log2 = P.scale_log2;
     int I = 0, Iq = 0, T = 0;
     bool ok = true;
+    // The merge + store of an item is deferred until this thread has finished the first tile of the
+    // next item: by then the item's last P V products are complete, so nobody waits for the tensor pipe.
+    bool pe_valid = false;
+    float pe_m = 0.f, pe_l = 0.f;
+    int pe_iq = 0, pe_tlast = 0, pe_tok0 = 0, pe_head0 = 0, pe_qend = 0;
+    EpilogueArgs ea;
+    ea.ctl = ctl; ea.o = P.o; ea.o_s0 = P.o_s0; ea.o_s1 = P.o_s1; ea.budget = budget; ea.trace = P.trace;
+    ea.abort_flag = abort_flag; ea.tOa = tOa; ea.tOb = tOb; ea.bar_pv_done_a = bar_pv_done_a; ea.bar_pv_done_b = bar_pv_done_b;
+    ea.bar_o_free = bar_o_free; ea.gp = P.gp; ea.gp_shift = P.gp_shift; ea.grp = grp; ea.has_b = has_b ? 1 : 0;
+    auto epilogue = [&]() -> bool {
+      ea.m = pe_m; ea.l = pe_l; ea.iq = pe_iq; ea.tlast = pe_tlast; ea.tok0 = pe_tok0; ea.head0 = pe_head0; ea.qend = pe_qend;
+      pe_valid = false;
+      return softmax_epilogue<D, BF16>(ea);
+    };
     while (ok) {
       ok = warp_wait(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
       if (!ok) break;
       const int n_tiles = slots[I & 1].n_tiles;
       if (n_tiles < 0) break;
-      const int r_tok = slots[I & 1].tile_tok0 + (row >> P.gp_shift);
-      const int r_head = slots[I & 1].head0 + (row & (P.gp - 1));
-      const bool r_valid = r_tok < slots[I & 1].q_end;
-      // each of the two threads of a row stores half of the head dimension
-      OutT* const orow = o_base + r_tok * P.o_s0 + r_head * P.o_s1 + grp * (D / 2);
       if (n_tiles == 0) {
+        if (pe_valid) { ok = epilogue(); if (!ok) break; }
         // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
-        if (r_valid) {
-          uint4* dst = reinterpret_cast<uint4*>(orow);
+        const int r_tok = slots[I & 1].tile_tok0 + (row >> P.gp_shift);
+        const int r_head = slots[I & 1].head0 + (row & (P.gp - 1));
+        if (r_tok < slots[I & 1].q_end) {
+          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + r_head * P.o_s1 + grp * (D / 2));
 #pragma unroll
           for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
         }
       } else {
+        const int it_tok0 = slots[I & 1].tile_tok0, it_head0 = slots[I & 1].head0, it_qend = slots[I & 1].q_end;
         int limit_row = slots[I & 1].k_len - 1;
         if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
@@ -596,75 +712,23 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
             if (lane == 0 && quarter == 0) stamp(P.trace, T, 9 + so);
+            if (t == 0 && pe_valid) { ok = epilogue(); if (!ok) break; }
           }
           if (!ok) break;
         } else {
+          if (pe_valid) { ok = epilogue(); if (!ok) break; }
           T += n_tiles;                              // group B without columns (16-row K/V tiles): nothing per tile
         }
-
-        // ---- merge of the two groups: (m, l) of both, O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)),
-        //      each thread of a row pair produces half of the head dimension; 16-byte stores, rows past the
-        //      q-block end are dropped
-        ctl->xm[Iq & 1][grp][row] = m_ref;
-        ctl->xl[Iq & 1][grp][row] = l;
-        __syncwarp();
-        {
-          const uint32_t pb = smem_u32(&ctl->pair[Iq & 1][quarter]);
-          if (lane == 0) mbar_arrive(pb);
-          ok = warp_wait(pb, par_of(Iq), abort_flag, budget);
-          if (!ok) break;
-        }
-        const float m_o = *reinterpret_cast<volatile float*>(&ctl->xm[Iq & 1][grp ^ 1][row]);
-        const float l_o = *reinterpret_cast<volatile float*>(&ctl->xl[Iq & 1][grp ^ 1][row]);
-        const float m_a = grp == 0 ? m_ref : m_o, m_b = grp == 0 ? m_o : m_ref;
-        const float l_a = grp == 0 ? l : l_o, l_b = grp == 0 ? l_o : l;
-        const float m_all = fmaxf(m_a, m_b);
-        const float w_a = m_a == -INFINITY ? 0.f : ex2_approx(m_a - m_all);
-        const float w_b = (!has_b || m_b == -INFINITY) ? 0.f : ex2_approx(m_b - m_all);
-        const float denom = l_a * w_a + l_b * w_b;
-        const bool live = denom > 0.f;                                      // rows that saw no key are exact zeros
-        const float f_a = live ? w_a / denom : 0.f, f_b = live ? w_b / denom : 0.f;
-        ok = warp_wait(bar_of(bar_pv_done_a, T - 1), par_of(T - 1), abort_flag, budget);
-        if (ok && has_b) ok = warp_wait(bar_of(bar_pv_done_b, T - 1), par_of(T - 1), abort_flag, budget);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
-          uint32_t oa[32], ob[32];
-          tmem_ld32(tOa + grp * (D / 2) + c0, oa);
-          if (has_b) tmem_ld32(tOb + grp * (D / 2) + c0, ob);
-          tmem_wait_ld();
-          if (c0 + 32 >= D / 2) {
-            tc_fence_before();                                             // both accumulators are in registers
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
-          }
-          if (r_valid) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + c0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int e = i * 8 + j * 2;
-                float x0 = __uint_as_float(oa[e]) * f_a, x1 = __uint_as_float(oa[e + 1]) * f_a;
-                if (has_b) {
-                  x0 = fmaf(__uint_as_float(ob[e]), f_b, x0);
-                  x1 = fmaf(__uint_as_float(ob[e + 1]), f_b, x1);
-                }
-                w[j] = live ? pack2<BF16>(x0, x1) : 0u;
-              }
-              dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
-        }
+        pe_valid = true;
+        pe_m = m_ref; pe_l = l; pe_iq = Iq; pe_tlast = T - 1;
+        pe_tok0 = it_tok0; pe_head0 = it_head0; pe_qend = it_qend;
         ++Iq;
       }
-      if (tid == 0) stamp(P.trace, T - 1, 11);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_of(bar_item_done, I));
       ++I;
     }
+    if (ok && pe_valid) epilogue();
   }
 
   // ---- teardown: every thread gets here (all waits are bounded)
