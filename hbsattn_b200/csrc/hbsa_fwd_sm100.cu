@@ -206,7 +206,7 @@ struct EpilogueArgs {
 // O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)); each thread of a row pair produces half
 // of the head dimension.  Kept out of line: it runs once per item from several places of the tile loop.
 template <int D, bool BF16>
-__device__ __noinline__ bool softmax_epilogue(const EpilogueArgs a) {
+__device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
   using namespace ptx;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(a.o);
@@ -604,8 +604,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float scale_log2 = P.scale_log2;
     int I = 0, Iq = 0, T = 0;
     bool ok = true;
-    // The merge + store of an item is deferred until this thread has finished the first tile of the
-    // next item: by then the item's last P V products are complete, so nobody waits for the tensor pipe.
+    // The merge + store of an item (softmax_epilogue) runs right after the item's last tile.
     bool pe_valid = false;
     float pe_m = 0.f, pe_l = 0.f;
     int pe_iq = 0, pe_tlast = 0, pe_tok0 = 0, pe_head0 = 0, pe_qend = 0;
@@ -712,7 +711,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
             if (lane == 0 && quarter == 0) stamp(P.trace, T, 9 + so);
-            if (t == 0 && pe_valid) { ok = epilogue(); if (!ok) break; }
           }
           if (!ok) break;
         } else {
@@ -722,6 +720,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         pe_valid = true;
         pe_m = m_ref; pe_l = l; pe_iq = Iq; pe_tlast = T - 1;
         pe_tok0 = it_tok0; pe_head0 = it_head0; pe_qend = it_qend;
+        ok = epilogue();
+        if (!ok) break;
         ++Iq;
       }
       __syncwarp();
