@@ -52,13 +52,26 @@ namespace hbsa {
 
 namespace {
 
-constexpr int kThreads = 384;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;          // issues S = Q K^T, owns the TMEM allocation
-constexpr int kPvWarpA = 10;         // issues O_A += P_A V
-constexpr int kPvWarpB = 11;         // issues O_B += P_B V
-constexpr int kTmemCols = 512;       // S0 [0,128)  S1 [128,256)  O_A [256,384)  O_B [384,512)
-constexpr int kTmemOCol = 256;
+// Two shapes of the same kernel:
+//  DUAL  : 384 threads, one CTA per SM, K/V tiles of up to 128 rows, two softmax groups (columns split),
+//          TMEM S0 [0,128) S1 [128,256) O_A [256,384) O_B [384,512), Q double-buffered.  Best for long rows.
+//  !DUAL : 224 threads, two CTAs per SM, K/V tiles of up to 64 rows, one softmax group (a thread owns a
+//          whole row of the tile), TMEM S0 [0,64) S1 [64,128) O [128,256), one Q buffer.  Two independent
+//          items are in flight per SM, which hides item boundaries: best for short rows.
+template <bool DUAL> struct Shape {
+  static constexpr int kSoftmaxWarps = DUAL ? 8 : 4;
+  static constexpr int kProducerWarp = kSoftmaxWarps;
+  static constexpr int kMmaWarp = kSoftmaxWarps + 1;      // issues S = Q K^T, owns the TMEM allocation
+  static constexpr int kPvWarpA = kSoftmaxWarps + 2;      // issues O_A += P_A V
+  static constexpr int kPvWarpB = kSoftmaxWarps + 3;      // issues O_B += P_B V (DUAL only)
+  static constexpr int kThreads = DUAL ? 384 : 224;
+  static constexpr int kCtasPerSm = DUAL ? 1 : 2;
+  static constexpr int kTmemCols = DUAL ? 512 : 256;
+  static constexpr uint32_t kSStride = DUAL ? 128u : 64u;   // TMEM columns between the two S buffers
+  static constexpr uint32_t kTmemOCol = DUAL ? 256u : 128u;
+  static constexpr int kTileRowsMax = DUAL ? 128 : 64;      // rows of a K/V tile
+  static constexpr int kQBuffers = DUAL ? 2 : 1;
+};
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct Sm100Params {
@@ -102,7 +115,8 @@ struct ItemSlot {
   int pad;
 };
 
-struct __align__(16) Control {
+template <bool DUAL>
+struct __align__(16) ControlT {
   unsigned long long item_full[2], item_done[2];
   unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], o_free[2];
   unsigned long long p_full[2][2], pv_done[2][2];      // [group][tile parity]
@@ -111,9 +125,9 @@ struct __align__(16) Control {
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
-  uint4 stage[8][32][4];     // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
-  float xm[2][2][128];       // [item parity][group][row]: reference maximum at the end of the item
-  float xl[2][2][128];       // [item parity][group][row]: row sum at the end of the item
+  uint4 stage[DUAL ? 8 : 4][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
+  float xm[DUAL ? 2 : 1][2][DUAL ? 128 : 1];   // [item parity][group][row]: reference maximum at the end of the item
+  float xl[DUAL ? 2 : 1][2][DUAL ? 128 : 1];   // [item parity][group][row]: row sum at the end of the item
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -142,12 +156,16 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
 // P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
+// (Computing a quarter of the exponentials with a polynomial on the FMA pipe was measured 15-20 % slower:
+// the softmax warps are short of issue slots, not of exp-unit throughput.)
 template <bool BF16>
 __device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[i]), scale_log2, neg_m));
-    const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m));
+    const float x0 = fmaf(__uint_as_float(r[i]), scale_log2, neg_m);
+    const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m);
+    const float p0 = ptx::ex2_approx(x0);
+    const float p1 = ptx::ex2_approx(x1);
     sum[(i >> 1) & 1] += p0;
     sum[2 + ((i >> 1) & 1)] += p1;
     pk[i >> 1] = pack2<BF16>(p0, p1);
@@ -191,7 +209,7 @@ __device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa
 
 // Arguments of the deferred merge + store of one work item (see softmax_epilogue).
 struct EpilogueArgs {
-  Control* ctl;
+  void* ctl_raw;
   void* o;
   long long o_s0, o_s1, budget;
   long long* trace;
@@ -205,26 +223,29 @@ struct EpilogueArgs {
 // Merge of the two softmax groups and store of one work item: with (m, l) of both groups,
 // O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)); each thread of a row pair produces half
 // of the head dimension.  Kept out of line: it runs once per item from several places of the tile loop.
-template <int D, bool BF16>
+template <int D, bool BF16, bool DUAL>
 __device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
+  constexpr int MY_COLS = DUAL ? D / 2 : D;            // head dims this thread produces
+  ControlT<DUAL>* const ctl_p = static_cast<ControlT<DUAL>*>(a.ctl_raw);
   using namespace ptx;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(a.o);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = tid & 127, quarter = warp & 3;
   bool ok = true;
-        a.ctl->xm[a.iq & 1][a.grp][row] = a.m;
-        a.ctl->xl[a.iq & 1][a.grp][row] = a.l;
-        __syncwarp();
-        {
-          const uint32_t pb = smem_u32(&a.ctl->pair[a.iq & 1][quarter]);
+        float m_o = -INFINITY, l_o = 0.f;
+        if (DUAL) {
+          ctl_p->xm[a.iq & 1][a.grp][row] = a.m;
+          ctl_p->xl[a.iq & 1][a.grp][row] = a.l;
+          __syncwarp();
+          const uint32_t pb = smem_u32(&ctl_p->pair[a.iq & 1][quarter]);
           if (lane == 0) mbar_arrive(pb);
           ok = warp_wait(pb, par_of(a.iq), a.abort_flag, a.budget);
           if (!ok) return false;
+          m_o = *reinterpret_cast<volatile float*>(&ctl_p->xm[a.iq & 1][a.grp ^ 1][row]);
+          l_o = *reinterpret_cast<volatile float*>(&ctl_p->xl[a.iq & 1][a.grp ^ 1][row]);
         }
         if (tid == 0) stamp(a.trace, a.tlast, 13);
-        const float m_o = *reinterpret_cast<volatile float*>(&a.ctl->xm[a.iq & 1][a.grp ^ 1][row]);
-        const float l_o = *reinterpret_cast<volatile float*>(&a.ctl->xl[a.iq & 1][a.grp ^ 1][row]);
         const float m_a = a.grp == 0 ? a.m : m_o, m_b = a.grp == 0 ? m_o : a.m;
         const float l_a = a.grp == 0 ? a.l : l_o, l_b = a.grp == 0 ? l_o : a.l;
         const float m_all = fmaxf(m_a, m_b);
@@ -240,12 +261,12 @@ __device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
         if (tid == 0) stamp(a.trace, a.tlast, 22);
         const int tile_tok0 = a.tok0, head0 = a.head0, q_end = a.qend;
 #pragma unroll
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        for (int c0 = 0; c0 < MY_COLS; c0 += 32) {
           uint32_t oa[32], ob[32];
-          tmem_ld32(a.tOa + a.grp * (D / 2) + c0, oa);
-          if (a.has_b) tmem_ld32(a.tOb + a.grp * (D / 2) + c0, ob);
+          tmem_ld32(a.tOa + a.grp * MY_COLS + c0, oa);
+          if (a.has_b) tmem_ld32(a.tOb + a.grp * MY_COLS + c0, ob);
           tmem_wait_ld();
-          if (c0 + 32 >= D / 2) {
+          if (c0 + 32 >= MY_COLS) {
             tc_fence_before();                                             // both accumulators are in registers
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(a.bar_o_free, a.iq));
@@ -254,7 +275,7 @@ __device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
           // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
           // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
           // below write whole 64-byte runs: four lanes per row, eight rows per instruction
-          uint4* const st = &a.ctl->stage[warp][0][0];
+          uint4* const st = &ctl_p->stage[warp][0][0];
           if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 24);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -280,7 +301,7 @@ __device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
             const int rg = quarter * 32 + rr;                               // row of the M tile
             const int tok = tile_tok0 + (rg >> a.gp_shift);
             if (tok < q_end) {
-              OutT* dst = o_base + tok * a.o_s0 + (head0 + (rg & (a.gp - 1))) * a.o_s1 + a.grp * (D / 2) + c0 + cc * 8;
+              OutT* dst = o_base + tok * a.o_s0 + (head0 + (rg & (a.gp - 1))) * a.o_s1 + a.grp * MY_COLS + c0 + cc * 8;
               *reinterpret_cast<uint4*>(dst) = val;
             }
           }
@@ -291,14 +312,20 @@ __device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
   return true;
 }
 
-template <int D, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, bool BF16, bool DUAL>
+__global__ void __launch_bounds__(Shape<DUAL>::kThreads, Shape<DUAL>::kCtasPerSm)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
   using namespace ptx;
+  using SH = Shape<DUAL>;
+  constexpr int kThreads = SH::kThreads, kProducerWarp = SH::kProducerWarp, kMmaWarp = SH::kMmaWarp;
+  constexpr int kPvWarpA = SH::kPvWarpA, kPvWarpB = SH::kPvWarpB, kTmemCols = SH::kTmemCols;
+  constexpr uint32_t kTmemOCol = SH::kTmemOCol, kSStride = SH::kSStride;
   constexpr int PANELS = D / 64;
   constexpr uint32_t Q_BYTES = 128u * D * 2u;
-  constexpr uint32_t KV_BYTES_MAX = 128u * D * 2u;
+  constexpr uint32_t KV_BYTES_MAX = (uint32_t)SH::kTileRowsMax * D * 2u;
+  constexpr int QBUF = SH::kQBuffers;
+  (void)kThreads;
   const Problem& p = P.p;
 
   if (P.ws.status[0] != HBSA_STATUS_OK) return;
@@ -306,7 +333,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(P.o);
-  const bool has_b = P.nt > P.ca;                  // group B owns at least one 16-column step
+  const bool has_b = DUAL && P.nt > P.ca;          // group B owns at least one 16-column step
 
   // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle)
   extern __shared__ uint8_t smem_raw[];
@@ -314,9 +341,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t* const smem = smem_raw + pad;
   const uint32_t sQ = raw_addr + pad;                 // 2 buffers
-  const uint32_t sK = sQ + 2 * Q_BYTES;               // 2 stages
+  const uint32_t sK = sQ + QBUF * Q_BYTES;            // 2 stages
   const uint32_t sV = sK + 2 * KV_BYTES_MAX;          // 2 stages
-  Control* const ctl = reinterpret_cast<Control*>(smem + 2 * Q_BYTES + 4 * KV_BYTES_MAX);
+  using Control = ControlT<DUAL>;
+  Control* const ctl = reinterpret_cast<Control*>(smem + QBUF * Q_BYTES + 4 * KV_BYTES_MAX);
   const uint32_t bar_item_full = smem_u32(&ctl->item_full[0]), bar_item_done = smem_u32(&ctl->item_done[0]);
   const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
   const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
@@ -330,12 +358,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_item_full + 8 * i, 1);
-      mbar_init(bar_item_done + 8 * i, 11);     // 8 softmax warps + the three MMA issuing threads
+      mbar_init(bar_item_done + 8 * i, SH::kSoftmaxWarps + (DUAL ? 3 : 2));   // softmax warps + the MMA issuing threads
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_k_full + 8 * i, 1);
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_o_free + 8 * i, 8);
+      mbar_init(bar_o_free + 8 * i, SH::kSoftmaxWarps);
       mbar_init(bar_p_full_a + 8 * i, 4);
       mbar_init(bar_p_full_b + 8 * i, 4);
       mbar_init(bar_pv_done_a + 8 * i, 1);
@@ -412,12 +440,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // issued in order, so this also means that the item that last used Q buffer Iq & 1 is through
       // with it (its last tile is T-2 or earlier).
       if (T >= 2) ok = warp_wait(bar_of(bar_s_full, T), par_of(T - 2), abort_flag, budget);
+      // with a single Q buffer the previous item's last S (tile T-1) must be done as well
+      if (ok && QBUF == 1 && T >= 1) ok = warp_wait(bar_of(bar_s_full, T - 1), par_of(T - 1), abort_flag, budget);
       if (!ok) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(bar_of(bar_q_full, Iq), Q_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(sQ + (Iq & 1) * Q_BYTES + pn * (128u * 128u), &tm_q, bar_of(bar_q_full, Iq), pn * 64, head0, tile_tok0);
+          tma_load_3d(sQ + (QBUF == 2 ? (Iq & 1) : 0) * Q_BYTES + pn * (128u * 128u), &tm_q, bar_of(bar_q_full, Iq), pn * 64, head0, tile_tok0);
       }
       ++Iq;
       const uint8_t* mrow = p.mask + rec.hk * p.mask_s0 + rec.qb * p.mask_s1;
@@ -487,7 +517,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
         const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
         qd0[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
-        qd1[ks] = smem_desc_join(smem_desc_lo(sQ + Q_BYTES, 16u) + qo, desc_hi);
+        qd1[ks] = smem_desc_join(smem_desc_lo(sQ + (QBUF == 2 ? Q_BYTES : 0u), 16u) + qo, desc_hi);
         kd0[ks] = smem_desc_join(smem_desc_lo(sK, 16u) + ko, desc_hi);
         kd1[ks] = smem_desc_join(smem_desc_lo(sK + KV_BYTES_MAX, 16u) + ko, desc_hi);
       }
@@ -510,7 +540,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             stamp(P.trace, T, 2);
-            const uint32_t tSb = tmem_base + (uint32_t)(T & 1) * 128u;
+            const uint32_t tSb = tmem_base + (uint32_t)(T & 1) * kSStride;
             if (Iq & 1) {
               if (T & 1) issue_qk<D / 16>(tSb, qd1, kd1, idesc_qk);
               else issue_qk<D / 16>(tSb, qd1, kd0, idesc_qk);
@@ -529,7 +559,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
     __syncwarp();
-  } else if (warp == kPvWarpA || warp == kPvWarpB) {
+  } else if (warp == kPvWarpA || (DUAL && warp == kPvWarpB)) {
     // =============================== issuers of O_g += P_g V ===============================
     if (lane == 0) {
       const int g = warp == kPvWarpA ? 0 : 1;
@@ -552,7 +582,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         vd1[i] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + ks * 128u, desc_hi);
         const uint32_t po = (g == 0 ? 0u : (uint32_t)P.ca) + (uint32_t)i * 8u;
         pa0[i] = tmem_base + po;
-        pa1[i] = tmem_base + 128u + po;
+        pa1[i] = tmem_base + kSStride + po;
       }
       int I = 0, Iq = 0, T = 0;
       bool ok = true;
@@ -589,7 +619,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
   } else {
     // =============================== softmax + epilogue ===============================
-    const int grp = tid >> 7;                        // 0: group A, columns [0, ca); 1: group B, columns [ca, nt)
+    const int grp = DUAL ? (tid >> 7) : 0;           // 0: group A, columns [0, ca); 1: group B, columns [ca, nt)
     const int row = tid & 127;
     const int quarter = warp & 3;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -609,13 +639,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float pe_m = 0.f, pe_l = 0.f;
     int pe_iq = 0, pe_tlast = 0, pe_tok0 = 0, pe_head0 = 0, pe_qend = 0;
     EpilogueArgs ea;
-    ea.ctl = ctl; ea.o = P.o; ea.o_s0 = P.o_s0; ea.o_s1 = P.o_s1; ea.budget = budget; ea.trace = P.trace;
+    ea.ctl_raw = ctl; ea.o = P.o; ea.o_s0 = P.o_s0; ea.o_s1 = P.o_s1; ea.budget = budget; ea.trace = P.trace;
     ea.abort_flag = abort_flag; ea.tOa = tOa; ea.tOb = tOb; ea.bar_pv_done_a = bar_pv_done_a; ea.bar_pv_done_b = bar_pv_done_b;
     ea.bar_o_free = bar_o_free; ea.gp = P.gp; ea.gp_shift = P.gp_shift; ea.grp = grp; ea.has_b = has_b ? 1 : 0;
     auto epilogue = [&]() -> bool {
       ea.m = pe_m; ea.l = pe_l; ea.iq = pe_iq; ea.tlast = pe_tlast; ea.tok0 = pe_tok0; ea.head0 = pe_head0; ea.qend = pe_qend;
       pe_valid = false;
-      return softmax_epilogue<D, BF16>(ea);
+      return softmax_epilogue<D, BF16, DUAL>(ea);
     };
     while (ok) {
       ok = warp_wait(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
@@ -630,7 +660,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (r_tok < slots[I & 1].q_end) {
           uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + r_head * P.o_s1 + grp * (D / 2));
 #pragma unroll
-          for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < (DUAL ? D / 16 : D / 8); ++i) dst[i] = make_uint4(0, 0, 0, 0);
         }
       } else {
         const int it_tok0 = slots[I & 1].tile_tok0, it_head0 = slots[I & 1].head0, it_qend = slots[I & 1].q_end;
@@ -645,7 +675,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tc_fence_after();
             if (lane == 0 && quarter == 0) stamp(P.trace, T, 6 + so);
             const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
-            const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * 128u + lane_off + (uint32_t)my_c0;
+            const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off + (uint32_t)my_c0;
 
             // ---- this thread's columns of S, all in registers
             uint32_t r[64];
@@ -795,9 +825,20 @@ int sm_count() {
 void sm100_set_trace(long long* device_buffer) { g_trace = device_buffer; }
 size_t sm100_trace_bytes() { return (size_t)kTraceTiles * kTraceSlots * sizeof(long long); }
 
+// Which shape of the kernel runs (see Shape<>): "dual" or "single"; HBSA_SM100_SHAPE overrides the default.
+bool sm100_dual_shape() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("HBSA_SM100_SHAPE");
+    cached = (e != nullptr && e[0] == 'd') ? 1 : 0;     // default: the single-group shape
+  }
+  return cached != 0;
+}
+
 int sm100_kv_tile_rows(int kbs) {
-  if (kbs <= 128) return kbs;
-  for (int nt = 128; nt >= 16; nt -= 16)
+  const int cap = sm100_dual_shape() ? 128 : 64;
+  if (kbs <= cap) return kbs;
+  for (int nt = cap; nt >= 16; nt -= 16)
     if (kbs % nt == 0) return nt;
   return 16;
 }
@@ -831,7 +872,8 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.o_s0 = a.o_stride[0];
   P.o_s1 = a.o_stride[1];
   P.nt = sm100_kv_tile_rows(p.kbs);
-  P.ca = ((P.nt / 16 + 1) / 2) * 16;                           // first half of the 16-column groups, rounded up
+  const bool dual = sm100_dual_shape();
+  P.ca = dual ? ((P.nt / 16 + 1) / 2) * 16 : P.nt;            // group A: first half of the 16-column groups, rounded up
   P.n_sub = p.kbs / P.nt;
   int gp = 1;
   while (gp < 128 && p.group % (gp * 2) == 0) gp *= 2;
@@ -848,7 +890,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
   if (P.total_items <= 0) { *err_text = "no work items"; return HBSA_ERR_SHAPE; }
-  const long long resident = sm_count();                        // one persistent CTA per SM
+  const long long resident = (long long)sm_count() * (dual ? 1 : 2);   // persistent CTAs
   const unsigned grid = (unsigned)(P.total_items < resident ? P.total_items : resident);
 
   CUtensorMap tq, tk, tv;
@@ -859,18 +901,23 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     return HBSA_ERR_UNSUPPORTED;
   }
 
-  const size_t smem = 6u * 128u * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
+  const size_t smem = (dual ? 6u * 128u : (128u + 4u * 64u)) * (size_t)p.headdim * 2u + (dual ? sizeof(ControlT<true>) : sizeof(ControlT<false>)) + 1024u;
   cudaError_t e = cudaSuccess;
-#define HBSA_LAUNCH_SM100(D_, BF_)                                                                        \
-  do {                                                                                                   \
-    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess) {                                                                              \
-      fwd_sm100_kernel<D_, BF_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                         \
-      e = cudaGetLastError();                                                                            \
-    }                                                                                                    \
+#define HBSA_LAUNCH_SM100(D_, BF_, DUAL_)                                                                  \
+  do {                                                                                                     \
+    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, DUAL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) {                                                                                \
+      fwd_sm100_kernel<D_, BF_, DUAL_><<<grid, Shape<DUAL_>::kThreads, smem, stream>>>(tq, tk, tv, P);     \
+      e = cudaGetLastError();                                                                              \
+    }                                                                                                      \
   } while (0)
-  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100(128, true); else HBSA_LAUNCH_SM100(128, false); }
-  else { if (bf16) HBSA_LAUNCH_SM100(64, true); else HBSA_LAUNCH_SM100(64, false); }
+#define HBSA_LAUNCH_SM100_D(D_)                                                                            \
+  do {                                                                                                     \
+    if (bf16) { if (dual) HBSA_LAUNCH_SM100(D_, true, true); else HBSA_LAUNCH_SM100(D_, true, false); }    \
+    else { if (dual) HBSA_LAUNCH_SM100(D_, false, true); else HBSA_LAUNCH_SM100(D_, false, false); }       \
+  } while (0)
+  if (p.headdim == 128) HBSA_LAUNCH_SM100_D(128); else HBSA_LAUNCH_SM100_D(64);
+#undef HBSA_LAUNCH_SM100_D
 #undef HBSA_LAUNCH_SM100
   if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return (int)e; }
   return 0;
