@@ -6,39 +6,37 @@
 //  * A work item is one 128-row M tile of one (kv-head, q-block): `TT = 128 / GP` tokens times
 //    `GP` q-heads of the GQA group packed into the MMA M dimension, so that one K/V tile fetch
 //    serves GP heads (the reference runs one program per q-head and re-reads K/V per head).
-//  * One persistent CTA per SM pulls work items from an atomic cursor over the ItemRecord table the
+//  * Persistent CTAs, two per SM, pull work items from an atomic cursor over the ItemRecord table the
 //    schedule kernels wrote; the producer warp publishes each item to the other warps through a
-//    two-slot ring in shared memory and runs up to one item ahead (Q is double-buffered).
+//    two-slot ring in shared memory and runs ahead of them.  Two CTAs per SM mean two independent
+//    items in flight, so the start and the end of one item hide behind the tiles of the other.
 //  * Only mask-active k-blocks are touched: the producer warp compacts the mask row with warp
-//    ballots and issues TMA loads of exactly those K/V tiles into two-stage K and V rings (the
-//    reference loops over all k-blocks of the sample and polls the mask byte,
+//    ballots and issues TMA loads of exactly those K/V tiles (at most 64 rows each) into two-stage K
+//    and V rings (the reference loops over all k-blocks of the sample and polls the mask byte,
 //    fwd_triton_fix_tile_size.py:117-124).
 //  * S = Q K^T and O += P V are tcgen05.mma instructions with fp32 accumulators in TMEM.  S is
 //    double-buffered, so S(t+1) is computed while the softmax warps work on S(t); P (in the input
 //    dtype, as at fwd_triton_fix_tile_size.py:187) is written back into TMEM over the S columns it
 //    came from and consumed as the A operand of the second MMA, so it never touches shared memory.
-//  * The columns of every tile are split between two softmax warpgroups that never talk to each
-//    other inside an item: group A owns columns [0, ca), group B columns [ca, nt), and each keeps
-//    its own online-softmax state (reference maximum, row sum) and its own output accumulator in
-//    TMEM (O_A, O_B) fed by its own P V products.  The two partial results are merged once per item
-//    in the epilogue, exactly like two key ranges of a split softmax.  Inside a group one thread
-//    owns one row: no shuffles, no shared-memory exchange per tile, and the two warps that share an
-//    SM sub-partition drift out of phase, so one of them keeps the exp unit busy while the other
-//    waits for TMEM.
+//    One thread issues every MMA; because tcgen05.mma instructions of one thread execute in issue
+//    order, S(t+2) is issued right behind P V(t) into the buffer that P(t) occupies without waiting
+//    for P V(t) to complete.
+//  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
+//    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
+//    and no shared-memory exchange.  The running output is rescaled in TMEM only when a row maximum
+//    grows by more than 2^8.
 //
-// Warp roles (384 threads): warps 0-3 softmax group A, warps 4-7 softmax group B (TMEM lane quarter
-// = warp id % 4), warp 8 work fetch + TMA producer, warp 9 TMEM allocator + issuer of S = Q K^T,
-// warps 10 and 11 issuers of the two groups' P V products.
+// Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp id), warp 4 work
+// fetch + TMA producer, warp 5 TMEM allocator + MMA issuer.  TMEM (256 columns): S0 [0,64), S1 [64,128),
+// O [128,256).
 //
 // mbarriers.  T counts K/V tiles over the whole life of the CTA, I counts published items, Iq those
 // of them that have tiles.  Two-entry barrier arrays are indexed by the low bit of the count and
 // complete once per use, so a waiter for count c uses entry c & 1 and parity (c >> 1) & 1:
 //   k_full / v_full [T]: TMA bytes landed          s_full [T]: S = Q K^T done (K stage free again)
-//   p_full [g][T]: group g wrote its P             pv_done [g][T]: O_g += P_g V done
-//                                                  (both groups done: V stage and S buffer free)
-//   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O_A, O_B out of TMEM
+//   p_full [T]: P written (one arrival per warp)   pv_done [T]: O += P V done (V stage free again)
+//   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O out of TMEM
 //   item_full [I]: item slot written               item_done [I]: all consumers left item I
-//   pair [Iq][quarter]: the two threads of a row exchanged (m, l) for the merge
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
@@ -52,26 +50,14 @@ namespace hbsa {
 
 namespace {
 
-// Two shapes of the same kernel:
-//  DUAL  : 384 threads, one CTA per SM, K/V tiles of up to 128 rows, two softmax groups (columns split),
-//          TMEM S0 [0,128) S1 [128,256) O_A [256,384) O_B [384,512), Q double-buffered.  Best for long rows.
-//  !DUAL : 224 threads, two CTAs per SM, K/V tiles of up to 64 rows, one softmax group (a thread owns a
-//          whole row of the tile), TMEM S0 [0,64) S1 [64,128) O [128,256), one Q buffer.  Two independent
-//          items are in flight per SM, which hides item boundaries: best for short rows.
-template <bool DUAL> struct Shape {
-  static constexpr int kSoftmaxWarps = DUAL ? 8 : 4;
-  static constexpr int kProducerWarp = kSoftmaxWarps;
-  static constexpr int kMmaWarp = kSoftmaxWarps + 1;      // issues S = Q K^T, owns the TMEM allocation
-  static constexpr int kPvWarpA = kSoftmaxWarps + 2;      // issues O_A += P_A V
-  static constexpr int kPvWarpB = kSoftmaxWarps + 3;      // issues O_B += P_B V (DUAL only)
-  static constexpr int kThreads = DUAL ? 384 : 224;
-  static constexpr int kCtasPerSm = DUAL ? 1 : 2;
-  static constexpr int kTmemCols = DUAL ? 512 : 256;
-  static constexpr uint32_t kSStride = DUAL ? 128u : 64u;   // TMEM columns between the two S buffers
-  static constexpr uint32_t kTmemOCol = DUAL ? 256u : 128u;
-  static constexpr int kTileRowsMax = DUAL ? 128 : 64;      // rows of a K/V tile
-  static constexpr int kQBuffers = DUAL ? 2 : 1;
-};
+constexpr int kThreads = 192;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kTileRowsMax = 64;      // rows of a K/V tile
+constexpr int kTmemCols = 256;
+constexpr uint32_t kSStride = 64u;    // TMEM columns between the two S buffers
+constexpr uint32_t kTmemOCol = 128u;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct Sm100Params {
@@ -79,8 +65,7 @@ struct Sm100Params {
   Workspace ws;
   void* o;
   long long o_s0, o_s1;        // elements
-  int nt;                      // rows of one K/V tile (multiple of 16, <= 128)
-  int ca;                      // columns [0, ca) of a tile belong to softmax group A, [ca, nt) to group B
+  int nt;                      // rows of one K/V tile (multiple of 16, <= 64)
   int n_sub;                   // K/V tiles per k-block
   int gp, gp_shift;            // q-heads packed into one M tile
   int n_head_sub;              // group / gp
@@ -95,10 +80,9 @@ struct Sm100Params {
 
 constexpr int kTraceTiles = 96;      // tiles of CTA 0 that are stamped
 constexpr int kTraceSlots = 32;      // stamps per tile
-// slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV_A(t) issue starts, 5 PV_A(t) issued,
-// 6 group A sees S, 7 A: row max done, 8 A: P written, 9 A: P arrival done, 10 item start (A), 11 A: epilogue done,
-// 12 A: S in registers, 14 PV_B(t) issue starts, 15 PV_B(t) issued, 16..21 the same as 6..9,12 for group B (16 sees S,
-// 17 max, 18 P written, 19 arrival, 20 S in registers)
+// slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV(t) issue starts, 5 PV(t) issued,
+// 6 softmax sees S, 7 row max done, 8 P written, 9 P arrival done, 10 item start, 11 epilogue done,
+// 12 S in registers, 13 epilogue starts, 22 last PV seen complete, 23 O in registers
 __device__ __forceinline__ void stamp(long long* trace, int tile, int slot) {
   if (trace != nullptr && blockIdx.x == 0 && tile >= 0 && tile < kTraceTiles) trace[tile * kTraceSlots + slot] = clock64();
 }
@@ -115,19 +99,14 @@ struct ItemSlot {
   int pad;
 };
 
-template <bool DUAL>
-struct __align__(16) ControlT {
+struct __align__(16) Control {
   unsigned long long item_full[2], item_done[2];
-  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], o_free[2];
-  unsigned long long p_full[2][2], pv_done[2][2];      // [group][tile parity]
-  unsigned long long pair[2][4];                       // [item parity][quarter]
+  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], o_free[2];
   uint32_t tmem_base;
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
-  uint4 stage[DUAL ? 8 : 4][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
-  float xm[DUAL ? 2 : 1][2][DUAL ? 128 : 1];   // [item parity][group][row]: reference maximum at the end of the item
-  float xl[DUAL ? 2 : 1][2][DUAL ? 128 : 1];   // [item parity][group][row]: row sum at the end of the item
+  uint4 stage[kSoftmaxWarps][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -156,16 +135,13 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
 // P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
-// (Computing a quarter of the exponentials with a polynomial on the FMA pipe was measured 15-20 % slower:
-// the softmax warps are short of issue slots, not of exp-unit throughput.)
+// (Computing a quarter of the exponentials with a polynomial on the FMA pipe was measured 15-20 % slower.)
 template <bool BF16>
 __device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const float x0 = fmaf(__uint_as_float(r[i]), scale_log2, neg_m);
-    const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m);
-    const float p0 = ptx::ex2_approx(x0);
-    const float p1 = ptx::ex2_approx(x1);
+    const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[i]), scale_log2, neg_m));
+    const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m));
     sum[(i >> 1) & 1] += p0;
     sum[2 + ((i >> 1) & 1)] += p1;
     pk[i >> 1] = pack2<BF16>(p0, p1);
@@ -207,125 +183,14 @@ __device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa
   }
 }
 
-// Arguments of the deferred merge + store of one work item (see softmax_epilogue).
-struct EpilogueArgs {
-  void* ctl_raw;
-  void* o;
-  long long o_s0, o_s1, budget;
-  long long* trace;
-  volatile int* abort_flag;
-  uint32_t tOa, tOb, bar_pv_done_a, bar_pv_done_b, bar_o_free;
-  int gp, gp_shift, grp, has_b;
-  float m, l;                 // this thread's reference maximum and row sum at the end of the item
-  int iq, tlast, tok0, head0, qend;
-};
-
-// Merge of the two softmax groups and store of one work item: with (m, l) of both groups,
-// O = (O_A 2^(mA-m) + O_B 2^(mB-m)) / (lA 2^(mA-m) + lB 2^(mB-m)); each thread of a row pair produces half
-// of the head dimension.  Kept out of line: it runs once per item from several places of the tile loop.
-template <int D, bool BF16, bool DUAL>
-__device__ __forceinline__ bool softmax_epilogue(const EpilogueArgs a) {
-  constexpr int MY_COLS = DUAL ? D / 2 : D;            // head dims this thread produces
-  ControlT<DUAL>* const ctl_p = static_cast<ControlT<DUAL>*>(a.ctl_raw);
-  using namespace ptx;
-  using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-  OutT* const o_base = static_cast<OutT*>(a.o);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row = tid & 127, quarter = warp & 3;
-  bool ok = true;
-        float m_o = -INFINITY, l_o = 0.f;
-        if (DUAL) {
-          ctl_p->xm[a.iq & 1][a.grp][row] = a.m;
-          ctl_p->xl[a.iq & 1][a.grp][row] = a.l;
-          __syncwarp();
-          const uint32_t pb = smem_u32(&ctl_p->pair[a.iq & 1][quarter]);
-          if (lane == 0) mbar_arrive(pb);
-          ok = warp_wait(pb, par_of(a.iq), a.abort_flag, a.budget);
-          if (!ok) return false;
-          m_o = *reinterpret_cast<volatile float*>(&ctl_p->xm[a.iq & 1][a.grp ^ 1][row]);
-          l_o = *reinterpret_cast<volatile float*>(&ctl_p->xl[a.iq & 1][a.grp ^ 1][row]);
-        }
-        if (tid == 0) stamp(a.trace, a.tlast, 13);
-        const float m_a = a.grp == 0 ? a.m : m_o, m_b = a.grp == 0 ? m_o : a.m;
-        const float l_a = a.grp == 0 ? a.l : l_o, l_b = a.grp == 0 ? l_o : a.l;
-        const float m_all = fmaxf(m_a, m_b);
-        const float w_a = m_a == -INFINITY ? 0.f : ex2_approx(m_a - m_all);
-        const float w_b = (!a.has_b || m_b == -INFINITY) ? 0.f : ex2_approx(m_b - m_all);
-        const float denom = l_a * w_a + l_b * w_b;
-        const bool live = denom > 0.f;                                      // rows that saw no key are exact zeros
-        const float f_a = live ? w_a / denom : 0.f, f_b = live ? w_b / denom : 0.f;
-        ok = warp_wait(bar_of(a.bar_pv_done_a, a.tlast), par_of(a.tlast), a.abort_flag, a.budget);
-        if (ok && a.has_b) ok = warp_wait(bar_of(a.bar_pv_done_b, a.tlast), par_of(a.tlast), a.abort_flag, a.budget);
-        if (!ok) return false;
-        tc_fence_after();
-        if (tid == 0) stamp(a.trace, a.tlast, 22);
-        const int tile_tok0 = a.tok0, head0 = a.head0, q_end = a.qend;
-#pragma unroll
-        for (int c0 = 0; c0 < MY_COLS; c0 += 32) {
-          uint32_t oa[32], ob[32];
-          tmem_ld32(a.tOa + a.grp * MY_COLS + c0, oa);
-          if (a.has_b) tmem_ld32(a.tOb + a.grp * MY_COLS + c0, ob);
-          tmem_wait_ld();
-          if (c0 + 32 >= MY_COLS) {
-            tc_fence_before();                                             // both accumulators are in registers
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_of(a.bar_o_free, a.iq));
-            if (tid == 0) stamp(a.trace, a.tlast, 23);
-          }
-          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
-          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
-          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
-          uint4* const st = &ctl_p->stage[warp][0][0];
-          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 24);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int e = i * 8 + j * 2;
-              float x0 = __uint_as_float(oa[e]) * f_a, x1 = __uint_as_float(oa[e + 1]) * f_a;
-              if (a.has_b) {
-                x0 = fmaf(__uint_as_float(ob[e]), f_b, x0);
-                x1 = fmaf(__uint_as_float(ob[e + 1]), f_b, x1);
-              }
-              w[j] = live ? pack2<BF16>(x0, x1) : 0u;
-            }
-            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          __syncwarp();
-          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 25);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
-            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
-            const int rg = quarter * 32 + rr;                               // row of the M tile
-            const int tok = tile_tok0 + (rg >> a.gp_shift);
-            if (tok < q_end) {
-              OutT* dst = o_base + tok * a.o_s0 + (head0 + (rg & (a.gp - 1))) * a.o_s1 + a.grp * MY_COLS + c0 + cc * 8;
-              *reinterpret_cast<uint4*>(dst) = val;
-            }
-          }
-          __syncwarp();
-          if (tid == 0 && c0 == 0) stamp(a.trace, a.tlast, 26);
-        }
-  if (tid == 0) stamp(a.trace, a.tlast, 11);
-  return true;
-}
-
-template <int D, bool BF16, bool DUAL>
-__global__ void __launch_bounds__(Shape<DUAL>::kThreads, Shape<DUAL>::kCtasPerSm)
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kThreads, 2)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
   using namespace ptx;
-  using SH = Shape<DUAL>;
-  constexpr int kThreads = SH::kThreads, kProducerWarp = SH::kProducerWarp, kMmaWarp = SH::kMmaWarp;
-  constexpr int kPvWarpA = SH::kPvWarpA, kPvWarpB = SH::kPvWarpB, kTmemCols = SH::kTmemCols;
-  constexpr uint32_t kTmemOCol = SH::kTmemOCol, kSStride = SH::kSStride;
   constexpr int PANELS = D / 64;
   constexpr uint32_t Q_BYTES = 128u * D * 2u;
-  constexpr uint32_t KV_BYTES_MAX = (uint32_t)SH::kTileRowsMax * D * 2u;
-  constexpr int QBUF = SH::kQBuffers;
-  (void)kThreads;
+  constexpr uint32_t KV_BYTES_MAX = (uint32_t)kTileRowsMax * D * 2u;
   const Problem& p = P.p;
 
   if (P.ws.status[0] != HBSA_STATUS_OK) return;
@@ -333,24 +198,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(P.o);
-  const bool has_b = DUAL && P.nt > P.ca;          // group B owns at least one 16-column step
 
   // ---- shared memory carve-up (1024-byte aligned tiles for the 128-byte swizzle)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t* const smem = smem_raw + pad;
-  const uint32_t sQ = raw_addr + pad;                 // 2 buffers
-  const uint32_t sK = sQ + QBUF * Q_BYTES;            // 2 stages
+  const uint32_t sQ = raw_addr + pad;
+  const uint32_t sK = sQ + Q_BYTES;                   // 2 stages
   const uint32_t sV = sK + 2 * KV_BYTES_MAX;          // 2 stages
-  using Control = ControlT<DUAL>;
-  Control* const ctl = reinterpret_cast<Control*>(smem + QBUF * Q_BYTES + 4 * KV_BYTES_MAX);
+  Control* const ctl = reinterpret_cast<Control*>(smem + Q_BYTES + 4 * KV_BYTES_MAX);
   const uint32_t bar_item_full = smem_u32(&ctl->item_full[0]), bar_item_done = smem_u32(&ctl->item_done[0]);
   const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
   const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
+  const uint32_t bar_p_full = smem_u32(&ctl->p_full[0]), bar_pv_done = smem_u32(&ctl->pv_done[0]);
   const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]);
-  const uint32_t bar_p_full_a = smem_u32(&ctl->p_full[0][0]), bar_p_full_b = smem_u32(&ctl->p_full[1][0]);
-  const uint32_t bar_pv_done_a = smem_u32(&ctl->pv_done[0][0]), bar_pv_done_b = smem_u32(&ctl->pv_done[1][0]);
   volatile int* const abort_flag = &ctl->abort_flag;
   volatile int* const tile_k0 = ctl->tile_k0;
   volatile ItemSlot* const slots = ctl->slot;
@@ -358,17 +220,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_item_full + 8 * i, 1);
-      mbar_init(bar_item_done + 8 * i, SH::kSoftmaxWarps + (DUAL ? 3 : 2));   // softmax warps + the MMA issuing threads
+      mbar_init(bar_item_done + 8 * i, kSoftmaxWarps + 1);      // softmax warps + the MMA thread
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_k_full + 8 * i, 1);
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_o_free + 8 * i, SH::kSoftmaxWarps);
-      mbar_init(bar_p_full_a + 8 * i, 4);
-      mbar_init(bar_p_full_b + 8 * i, 4);
-      mbar_init(bar_pv_done_a + 8 * i, 1);
-      mbar_init(bar_pv_done_b + 8 * i, 1);
-      for (int qd = 0; qd < 4; ++qd) mbar_init(smem_u32(&ctl->pair[i][qd]), 2);
+      mbar_init(bar_p_full + 8 * i, kSoftmaxWarps);
+      mbar_init(bar_pv_done + 8 * i, 1);
+      mbar_init(bar_o_free + 8 * i, kSoftmaxWarps);
     }
     ctl->abort_flag = 0;
     fence_barrier_init();
@@ -436,18 +295,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!have) break;
       if (n_tiles <= 0) continue;
 
-      // The first K tile of the item goes to stage T & 1, free once S(T-2) is done; the S products are
-      // issued in order, so this also means that the item that last used Q buffer Iq & 1 is through
-      // with it (its last tile is T-2 or earlier).
-      if (T >= 2) ok = warp_wait(bar_of(bar_s_full, T), par_of(T - 2), abort_flag, budget);
-      // with a single Q buffer the previous item's last S (tile T-1) must be done as well
-      if (ok && QBUF == 1 && T >= 1) ok = warp_wait(bar_of(bar_s_full, T - 1), par_of(T - 1), abort_flag, budget);
+      // Q has one buffer: the previous item's last S (tile T-1) must be done.  S products complete in
+      // order, so this covers tile T-2 (whose K stage the first tile of this item reuses) as well.
+      if (T >= 1) ok = warp_wait(bar_of(bar_s_full, T - 1), par_of(T - 1), abort_flag, budget);
       if (!ok) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(bar_of(bar_q_full, Iq), Q_BYTES);
 #pragma unroll
         for (int pn = 0; pn < PANELS; ++pn)
-          tma_load_3d(sQ + (QBUF == 2 ? (Iq & 1) : 0) * Q_BYTES + pn * (128u * 128u), &tm_q, bar_of(bar_q_full, Iq), pn * 64, head0, tile_tok0);
+          tma_load_3d(sQ + pn * (128u * 128u), &tm_q, bar_of(bar_q_full, Iq), pn * 64, head0, tile_tok0);
       }
       ++Iq;
       const uint8_t* mrow = p.mask + rec.hk * p.mask_s0 + rec.qb * p.mask_s1;
@@ -476,11 +332,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 tma_load_3d(sK + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_k, bar_of(bar_k_full, T), pn * 64, rec.hk, rec.k_begin + k0);
               stamp(P.trace, T, 0);
             }
-            // V stage T & 1 is free once both groups' P V products of tile T-2 are done
-            if (T >= 2) {
-              ok = warp_wait(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
-              if (ok && has_b) ok = warp_wait(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
-            }
+            // V stage T & 1 is free once the P V product of tile T-2 is done
+            if (T >= 2) ok = warp_wait(bar_of(bar_pv_done, T), par_of(T - 2), abort_flag, budget);
             if (!ok) break;
             if (lane == 0) {
               mbar_arrive_expect_tx(bar_of(bar_v_full, T), kv_tile_bytes);
@@ -502,263 +355,270 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
   } else if (warp == kMmaWarp) {
-    // =============================== issuer of S = Q K^T ===============================
-    // tcgen05.mma costs the lone issuing thread ~50 clocks apiece (more when its SM sub-partition is
-    // busy), about what the tensor pipe needs to execute one, so the three kinds of products are
-    // issued by three threads on three sub-partitions, each blocking on exactly its own barriers.
+    // =============================== MMA issuer ===============================
+    // One thread issues every tcgen05.mma of the CTA in the order S(0), S(1), PV(0), S(2), PV(1), S(3), ...
+    // S(t+2) goes into the buffer that P(t) occupies and is issued right behind PV(t) without waiting for
+    // PV(t) to complete: instructions of one thread execute in issue order, so PV(t) has read P(t) before
+    // S(t+2) writes.  The thread polls with non-blocking probes and issues whichever of "next P V" / "next
+    // S" has its inputs ready; a clock budget bounds the loop.
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(BF16, false, false, 128, P.nt);
+      const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
+      const int ksteps = P.nt >> 4;
       const uint32_t desc_hi = smem_desc_hi(1024u);
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
       // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
-      uint64_t qd0[8], qd1[8], kd0[8], kd1[8];
+      // V is MN-major: 16 keys further = 2048 bytes = 128 units.  P: 8 TMEM columns per 16 keys.
+      uint64_t qd[8], kd0[8], kd1[8], vd0[4], vd1[4];
+      uint32_t pa0[4], pa1[4];
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
         const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
-        qd0[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
-        qd1[ks] = smem_desc_join(smem_desc_lo(sQ + (QBUF == 2 ? Q_BYTES : 0u), 16u) + qo, desc_hi);
+        qd[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
         kd0[ks] = smem_desc_join(smem_desc_lo(sK, 16u) + ko, desc_hi);
         kd1[ks] = smem_desc_join(smem_desc_lo(sK + KV_BYTES_MAX, 16u) + ko, desc_hi);
       }
-      int I = 0, Iq = 0, T = 0;
-      bool ok = true;
-      while (ok) {
-        ok = mbar_wait_bounded(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
-        if (!ok) break;
-        const int n_tiles = slots[I & 1].n_tiles;
-        if (n_tiles < 0) break;
-        if (n_tiles > 0) {
-          ok = mbar_wait_bounded(bar_of(bar_q_full, Iq), par_of(Iq), abort_flag, budget);
-          for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-            ok = mbar_spin_bounded(bar_of(bar_k_full, T), par_of(T), abort_flag, budget);
-            // S buffer T & 1 held P(T-2): free once both groups' P V products of tile T-2 are done
-            if (ok && T >= 2) {
-              ok = mbar_spin_bounded(bar_of(bar_pv_done_a, T), par_of(T - 2), abort_flag, budget);
-              if (ok && has_b) ok = mbar_spin_bounded(bar_of(bar_pv_done_b, T), par_of(T - 2), abort_flag, budget);
-            }
-            if (!ok) break;
-            tc_fence_after();
-            stamp(P.trace, T, 2);
-            const uint32_t tSb = tmem_base + (uint32_t)(T & 1) * kSStride;
-            if (Iq & 1) {
-              if (T & 1) issue_qk<D / 16>(tSb, qd1, kd1, idesc_qk);
-              else issue_qk<D / 16>(tSb, qd1, kd0, idesc_qk);
-            } else {
-              if (T & 1) issue_qk<D / 16>(tSb, qd0, kd1, idesc_qk);
-              else issue_qk<D / 16>(tSb, qd0, kd0, idesc_qk);
-            }
-            tc_commit(bar_of(bar_s_full, T));
-            stamp(P.trace, T, 3);
-          }
-          ++Iq;
-        }
-        if (!ok) break;
-        mbar_arrive(bar_of(bar_item_done, I));
-        ++I;
-      }
-    }
-    __syncwarp();
-  } else if (warp == kPvWarpA || (DUAL && warp == kPvWarpB)) {
-    // =============================== issuers of O_g += P_g V ===============================
-    if (lane == 0) {
-      const int g = warp == kPvWarpA ? 0 : 1;
-      const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
-      const uint32_t desc_hi = smem_desc_hi(1024u);
-      const int ca_steps = P.ca >> 4;
-      const int k_first = g == 0 ? 0 : ca_steps;                     // this group's 16-key steps of a tile
-      const int n_steps = g == 0 ? ca_steps : (P.nt >> 4) - ca_steps;
-      const uint32_t bar_p_full = g == 0 ? bar_p_full_a : bar_p_full_b;
-      const uint32_t bar_pv_done = g == 0 ? bar_pv_done_a : bar_pv_done_b;
-      const uint32_t tOg = tmem_base + kTmemOCol + (uint32_t)g * 128u;
-      // V is MN-major: 16 keys further = 2048 bytes = 128 descriptor units.  P: 8 TMEM columns per 16 keys,
-      // group A's at S + 0.., group B's at S + ca..
-      uint64_t vd0[4], vd1[4];
-      uint32_t pa0[4], pa1[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t ks = (uint32_t)(k_first + i);
-        vd0[i] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + ks * 128u, desc_hi);
-        vd1[i] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + ks * 128u, desc_hi);
-        const uint32_t po = (g == 0 ? 0u : (uint32_t)P.ca) + (uint32_t)i * 8u;
-        pa0[i] = tmem_base + po;
-        pa1[i] = tmem_base + kSStride + po;
+      for (int ks = 0; ks < 4; ++ks) {
+        vd0[ks] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        vd1[ks] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        pa0[ks] = tmem_base + (uint32_t)ks * 8u;
+        pa1[ks] = tmem_base + kSStride + (uint32_t)ks * 8u;
       }
-      int I = 0, Iq = 0, T = 0;
-      bool ok = true;
-      while (ok) {
-        ok = mbar_wait_bounded(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
-        if (!ok) break;
-        const int n_tiles = slots[I & 1].n_tiles;
-        if (n_tiles < 0) break;
-        if (n_tiles > 0) {
-          if (n_steps > 0) {
-            for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-              ok = mbar_spin_bounded(bar_of(bar_v_full, T), par_of(T), abort_flag, budget);
-              if (ok) ok = mbar_spin_bounded(bar_of(bar_p_full, T), par_of(T), abort_flag, budget);
-              // the first P V of an item overwrites O: the epilogue of the previous item must have read it
-              if (ok && t == 0 && Iq >= 1) ok = mbar_wait_bounded(bar_of(bar_o_free, Iq - 1), par_of(Iq - 1), abort_flag, budget);
-              if (!ok) break;
-              tc_fence_after();
-              stamp(P.trace, T, g == 0 ? 4 : 14);
-              if (T & 1) issue_pv(n_steps, tOg, pa1, vd1, idesc_pv, t == 0);
-              else issue_pv(n_steps, tOg, pa0, vd0, idesc_pv, t == 0);
-              tc_commit(bar_of(bar_pv_done, T));
-              stamp(P.trace, T, g == 0 ? 5 : 15);
-            }
+      const uint32_t tO = tmem_base + kTmemOCol;
+      // S side: item qI (count of published items), its tiles left, number of items with tiles so far, next tile
+      int qI = 0, q_left = 0, qIq = 0, qT = 0;
+      bool q_have = false, q_first = false, finished = false;
+      // P V side: the items whose tiles are in flight, per tile "first of its item" / "last of its item"
+      int pT = 0;                    // next tile to issue P V for (pT <= qT <= pT + 2)
+      int pIq = 0;                   // items with tiles whose first P V has been issued
+      int fl_first[2] = {0, 0}, fl_last[2] = {0, 0}, fl_item[2] = {0, 0};   // indexed by tile & 1
+      long long t_progress = clock64();
+      while (true) {
+        bool progress = false;
+        if (!q_have && !finished && mbar_test(bar_of(bar_item_full, qI), par_of(qI))) {
+          const int n_tiles = slots[qI & 1].n_tiles;
+          if (n_tiles < 0) {
+            finished = true;
+          } else if (n_tiles == 0) {
+            mbar_arrive(bar_of(bar_item_done, qI));
+            ++qI;
           } else {
-            T += n_tiles;
+            q_have = true;
+            q_first = true;
+            q_left = n_tiles;
           }
-          ++Iq;
+          progress = true;
         }
-        if (!ok) break;
-        mbar_arrive(bar_of(bar_item_done, I));
-        ++I;
+        if (pT < qT) {
+          bool ready = mbar_test(bar_of(bar_p_full, pT), par_of(pT)) && mbar_test(bar_of(bar_v_full, pT), par_of(pT));
+          // the first P V of an item overwrites O: the epilogue of the previous item must have read it
+          if (ready && fl_first[pT & 1] && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
+          if (ready) {
+            tc_fence_after();
+            stamp(P.trace, pT, 4);
+            if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
+            else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
+            tc_commit(bar_of(bar_pv_done, pT));
+            stamp(P.trace, pT, 5);
+            if (fl_first[pT & 1]) ++pIq;
+            if (fl_last[pT & 1]) mbar_arrive(bar_of(bar_item_done, fl_item[pT & 1]));   // through with the item
+            ++pT;
+            progress = true;
+          }
+        }
+        if (q_have && qT < pT + 2) {
+          bool ready = mbar_test(bar_of(bar_k_full, qT), par_of(qT));
+          if (ready && q_first) ready = mbar_test(bar_of(bar_q_full, qIq), par_of(qIq));
+          if (ready) {
+            tc_fence_after();
+            stamp(P.trace, qT, 2);
+            const uint32_t tSb = tmem_base + (uint32_t)(qT & 1) * kSStride;
+            if (qT & 1) issue_qk<D / 16>(tSb, qd, kd1, idesc_qk);
+            else issue_qk<D / 16>(tSb, qd, kd0, idesc_qk);
+            tc_commit(bar_of(bar_s_full, qT));
+            stamp(P.trace, qT, 3);
+            fl_first[qT & 1] = q_first ? 1 : 0;
+            fl_last[qT & 1] = q_left == 1 ? 1 : 0;
+            fl_item[qT & 1] = qI;
+            ++qT;
+            if (q_first) ++qIq;
+            q_first = false;
+            if (--q_left == 0) {
+              ++qI;
+              q_have = false;
+            }
+            progress = true;
+          }
+        }
+        if (finished && pT == qT) break;
+        if (progress) {
+          t_progress = clock64();
+        } else {
+          if (*abort_flag) break;
+          if (clock64() - t_progress > budget) { *abort_flag = 1; break; }
+        }
       }
     }
     __syncwarp();
   } else {
     // =============================== softmax + epilogue ===============================
-    const int grp = DUAL ? (tid >> 7) : 0;           // 0: group A, columns [0, ca); 1: group B, columns [ca, nt)
-    const int row = tid & 127;
-    const int quarter = warp & 3;
-    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const int my_c0 = grp == 0 ? 0 : P.ca;           // first tile column of this thread
-    const int my_nc = grp == 0 ? P.ca : P.nt - P.ca; // columns of this thread: 0, 16, 32, 48 or 64
-    const bool active = my_nc > 0;
-    const uint32_t bar_p_full = grp == 0 ? bar_p_full_a : bar_p_full_b;
-    const uint32_t bar_pv_done = grp == 0 ? bar_pv_done_a : bar_pv_done_b;
-    const uint32_t tOmine = tmem_base + kTmemOCol + (uint32_t)grp * 128u + lane_off;   // this group's accumulator
-    const uint32_t tOa = tmem_base + kTmemOCol + lane_off, tOb = tOa + 128u;
-    const int so = grp * 6 + (grp ? 4 : 0);          // trace slot offset: group A 6.., group B 16..
+    const int row = tid;                             // 0..127: row of the M tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const int my_nc = P.nt;                          // columns of a tile: 16, 32, 48 or 64
+    const uint32_t tOmine = tmem_base + kTmemOCol + lane_off;
     const float scale_log2 = P.scale_log2;
     int I = 0, Iq = 0, T = 0;
     bool ok = true;
-    // The merge + store of an item (softmax_epilogue) runs right after the item's last tile.
-    bool pe_valid = false;
-    float pe_m = 0.f, pe_l = 0.f;
-    int pe_iq = 0, pe_tlast = 0, pe_tok0 = 0, pe_head0 = 0, pe_qend = 0;
-    EpilogueArgs ea;
-    ea.ctl_raw = ctl; ea.o = P.o; ea.o_s0 = P.o_s0; ea.o_s1 = P.o_s1; ea.budget = budget; ea.trace = P.trace;
-    ea.abort_flag = abort_flag; ea.tOa = tOa; ea.tOb = tOb; ea.bar_pv_done_a = bar_pv_done_a; ea.bar_pv_done_b = bar_pv_done_b;
-    ea.bar_o_free = bar_o_free; ea.gp = P.gp; ea.gp_shift = P.gp_shift; ea.grp = grp; ea.has_b = has_b ? 1 : 0;
-    auto epilogue = [&]() -> bool {
-      ea.m = pe_m; ea.l = pe_l; ea.iq = pe_iq; ea.tlast = pe_tlast; ea.tok0 = pe_tok0; ea.head0 = pe_head0; ea.qend = pe_qend;
-      pe_valid = false;
-      return softmax_epilogue<D, BF16, DUAL>(ea);
-    };
     while (ok) {
       ok = warp_wait(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
       if (!ok) break;
       const int n_tiles = slots[I & 1].n_tiles;
       if (n_tiles < 0) break;
+      const int tile_tok0 = slots[I & 1].tile_tok0, head0 = slots[I & 1].head0, q_end = slots[I & 1].q_end;
       if (n_tiles == 0) {
-        if (pe_valid) { ok = epilogue(); if (!ok) break; }
         // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
-        const int r_tok = slots[I & 1].tile_tok0 + (row >> P.gp_shift);
-        const int r_head = slots[I & 1].head0 + (row & (P.gp - 1));
-        if (r_tok < slots[I & 1].q_end) {
-          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + r_head * P.o_s1 + grp * (D / 2));
+        const int r_tok = tile_tok0 + (row >> P.gp_shift);
+        if (r_tok < q_end) {
+          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
 #pragma unroll
-          for (int i = 0; i < (DUAL ? D / 16 : D / 8); ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
         }
       } else {
-        const int it_tok0 = slots[I & 1].tile_tok0, it_head0 = slots[I & 1].head0, it_qend = slots[I & 1].q_end;
         int limit_row = slots[I & 1].k_len - 1;
         if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
         if (tid == 0) stamp(P.trace, T, 10);
-        if (active) {
-          for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-            ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0 && quarter == 0) stamp(P.trace, T, 6 + so);
-            const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
-            const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off + (uint32_t)my_c0;
+        for (int t = 0; t < n_tiles && ok; ++t, ++T) {
+          ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
+          if (!ok) break;
+          tc_fence_after();
+          if (tid == 0) stamp(P.trace, T, 6);
+          const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
+          const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off;
 
-            // ---- this thread's columns of S, all in registers
-            uint32_t r[64];
+          // ---- this thread's row of S, all in registers
+          uint32_t r[64];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
-            tmem_wait_ld();
-            if (lane == 0 && quarter == 0) stamp(P.trace, T, 12 + (grp ? 8 : 0));
-            if (col_limit < my_c0 + my_nc - 1) {
-              // tile on the causal diagonal or at the ragged end of the sample: mask in place
+          for (int j = 0; j < 4; ++j)
+            if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
+          tmem_wait_ld();
+          if (tid == 0) stamp(P.trace, T, 12);
+          if (col_limit < my_nc - 1) {
+            // tile on the causal diagonal or at the ragged end of the sample: mask in place
 #pragma unroll
-              for (int i = 0; i < 64; ++i)
-                if (my_c0 + i > col_limit) r[i] = 0xff800000u;             // -inf
-            }
+            for (int i = 0; i < 64; ++i)
+              if (i > col_limit) r[i] = 0xff800000u;                     // -inf
+          }
 
-            // ---- row maximum over this group's columns only
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          // ---- row maximum
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (my_nc > 16 * j) max16(&r[16 * j], mx4);
-            const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
-            if (lane == 0 && quarter == 0) stamp(P.trace, T, 7 + so);
-            if (t == 0) {
-              m_ref = mx_s;
-            } else {
-              const bool need = mx_s > m_ref + kRescaleThreshold;
-              if (__any_sync(0xffffffffu, need)) {
-                // this group's O and l move to the new reference maximum; needs its P V of the previous tile
-                ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
-                if (!ok) break;
-                tc_fence_after();
-                const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
+          for (int j = 0; j < 4; ++j)
+            if (my_nc > 16 * j) max16(&r[16 * j], mx4);
+          const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
+          if (tid == 0) stamp(P.trace, T, 7);
+          if (t == 0) {
+            m_ref = mx_s;
+          } else {
+            const bool need = mx_s > m_ref + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, need)) {
+              // O and l move to the new reference maximum; needs the P V product of the previous tile
+              ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+              if (!ok) break;
+              tc_fence_after();
+              const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                  uint32_t o[32];
-                  tmem_ld32(tOmine + c0, o);
-                  tmem_wait_ld();
+              for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tOmine + c0, o);
+                tmem_wait_ld();
 #pragma unroll
-                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                  tmem_st32(tOmine + c0, o);
-                }
-                tmem_wait_st();
-                l *= alpha;
-                if (need) m_ref = mx_s;
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st32(tOmine + c0, o);
               }
+              tmem_wait_st();
+              l *= alpha;
+              if (need) m_ref = mx_s;
             }
-            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+          }
+          const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
 
-            // ---- P = exp2(S * scale - m) packed to 16 bit over this thread's own S columns, row sum
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (my_nc > 16 * j) {
+              uint32_t pk[8];
+              exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+              tmem_st8(tSmine + 8 * j, pk);
+            }
+          }
+          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          tmem_wait_st();
+          tc_fence_before();
+          if (tid == 0) stamp(P.trace, T, 8);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
+          if (tid == 0) stamp(P.trace, T, 9);
+        }
+        if (!ok) break;
+
+        // ---- epilogue: O / l -> global; rows past the q-block end are dropped, rows that saw no key are zeros
+        if (tid == 0) stamp(P.trace, T - 1, 13);
+        const bool live = l > 0.f;
+        const float inv = live ? 1.f / l : 0.f;
+        ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+        if (!ok) break;
+        tc_fence_after();
+        if (tid == 0) stamp(P.trace, T - 1, 22);
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t oa[32];
+          tmem_ld32(tOmine + c0, oa);
+          tmem_wait_ld();
+          if (c0 + 32 >= D) {
+            tc_fence_before();                                             // O is in registers: the next item may overwrite it
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
+            if (tid == 0) stamp(P.trace, T - 1, 23);
+          }
+          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
+          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
+          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
+          uint4* const st = &ctl->stage[warp][0][0];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (my_nc > 16 * j) {
-                uint32_t pk[8];
-                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
-                tmem_st8(tSmine + 8 * j, pk);
-              }
+              const int e = i * 8 + j * 2;
+              w[j] = live ? pack2<BF16>(__uint_as_float(oa[e]) * inv, __uint_as_float(oa[e + 1]) * inv) : 0u;
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            tmem_wait_st();
-            tc_fence_before();
-            if (lane == 0 && quarter == 0) stamp(P.trace, T, 8 + so);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
-            if (lane == 0 && quarter == 0) stamp(P.trace, T, 9 + so);
+            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if (!ok) break;
-        } else {
-          if (pe_valid) { ok = epilogue(); if (!ok) break; }
-          T += n_tiles;                              // group B without columns (16-row K/V tiles): nothing per tile
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
+            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
+            const int rg = warp * 32 + rr;                                  // row of the M tile
+            const int tok = tile_tok0 + (rg >> P.gp_shift);
+            if (tok < q_end) {
+              OutT* dst = o_base + tok * P.o_s0 + (head0 + (rg & (P.gp - 1))) * P.o_s1 + c0 + cc * 8;
+              *reinterpret_cast<uint4*>(dst) = val;
+            }
+          }
+          __syncwarp();
         }
-        pe_valid = true;
-        pe_m = m_ref; pe_l = l; pe_iq = Iq; pe_tlast = T - 1;
-        pe_tok0 = it_tok0; pe_head0 = it_head0; pe_qend = it_qend;
-        ok = epilogue();
-        if (!ok) break;
+        if (tid == 0) stamp(P.trace, T - 1, 11);
         ++Iq;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_of(bar_item_done, I));
       ++I;
     }
-    if (ok && pe_valid) epilogue();
   }
 
   // ---- teardown: every thread gets here (all waits are bounded)
@@ -825,20 +685,9 @@ int sm_count() {
 void sm100_set_trace(long long* device_buffer) { g_trace = device_buffer; }
 size_t sm100_trace_bytes() { return (size_t)kTraceTiles * kTraceSlots * sizeof(long long); }
 
-// Which shape of the kernel runs (see Shape<>): "dual" or "single"; HBSA_SM100_SHAPE overrides the default.
-bool sm100_dual_shape() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("HBSA_SM100_SHAPE");
-    cached = (e != nullptr && e[0] == 'd') ? 1 : 0;     // default: the single-group shape
-  }
-  return cached != 0;
-}
-
 int sm100_kv_tile_rows(int kbs) {
-  const int cap = sm100_dual_shape() ? 128 : 64;
-  if (kbs <= cap) return kbs;
-  for (int nt = cap; nt >= 16; nt -= 16)
+  if (kbs <= kTileRowsMax) return kbs;
+  for (int nt = kTileRowsMax; nt >= 16; nt -= 16)
     if (kbs % nt == 0) return nt;
   return 16;
 }
@@ -872,8 +721,6 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.o_s0 = a.o_stride[0];
   P.o_s1 = a.o_stride[1];
   P.nt = sm100_kv_tile_rows(p.kbs);
-  const bool dual = sm100_dual_shape();
-  P.ca = dual ? ((P.nt / 16 + 1) / 2) * 16 : P.nt;            // group A: first half of the 16-column groups, rounded up
   P.n_sub = p.kbs / P.nt;
   int gp = 1;
   while (gp < 128 && p.group % (gp * 2) == 0) gp *= 2;
@@ -890,7 +737,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
   if (P.total_items <= 0) { *err_text = "no work items"; return HBSA_ERR_SHAPE; }
-  const long long resident = (long long)sm_count() * (dual ? 1 : 2);   // persistent CTAs
+  const long long resident = 2ll * sm_count();                  // two persistent CTAs per SM
   const unsigned grid = (unsigned)(P.total_items < resident ? P.total_items : resident);
 
   CUtensorMap tq, tk, tv;
@@ -901,23 +748,18 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     return HBSA_ERR_UNSUPPORTED;
   }
 
-  const size_t smem = (dual ? 6u * 128u : (128u + 4u * 64u)) * (size_t)p.headdim * 2u + (dual ? sizeof(ControlT<true>) : sizeof(ControlT<false>)) + 1024u;
+  const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
-#define HBSA_LAUNCH_SM100(D_, BF_, DUAL_)                                                                  \
-  do {                                                                                                     \
-    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, DUAL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess) {                                                                                \
-      fwd_sm100_kernel<D_, BF_, DUAL_><<<grid, Shape<DUAL_>::kThreads, smem, stream>>>(tq, tk, tv, P);     \
-      e = cudaGetLastError();                                                                              \
-    }                                                                                                      \
+#define HBSA_LAUNCH_SM100(D_, BF_)                                                                        \
+  do {                                                                                                   \
+    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) {                                                                              \
+      fwd_sm100_kernel<D_, BF_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                        \
+      e = cudaGetLastError();                                                                            \
+    }                                                                                                    \
   } while (0)
-#define HBSA_LAUNCH_SM100_D(D_)                                                                            \
-  do {                                                                                                     \
-    if (bf16) { if (dual) HBSA_LAUNCH_SM100(D_, true, true); else HBSA_LAUNCH_SM100(D_, true, false); }    \
-    else { if (dual) HBSA_LAUNCH_SM100(D_, false, true); else HBSA_LAUNCH_SM100(D_, false, false); }       \
-  } while (0)
-  if (p.headdim == 128) HBSA_LAUNCH_SM100_D(128); else HBSA_LAUNCH_SM100_D(64);
-#undef HBSA_LAUNCH_SM100_D
+  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100(128, true); else HBSA_LAUNCH_SM100(128, false); }
+  else { if (bf16) HBSA_LAUNCH_SM100(64, true); else HBSA_LAUNCH_SM100(64, false); }
 #undef HBSA_LAUNCH_SM100
   if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return (int)e; }
   return 0;
