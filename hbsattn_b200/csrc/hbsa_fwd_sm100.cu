@@ -416,7 +416,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // the first P V of an item overwrites O: the epilogue of the previous item must have read it
           if (ready && fl_first[pT & 1] && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
           if (ready) {
-            tc_fence_after();
+            // No tcgen05.fence::after_thread_sync here: it was measured to stall this thread until the MMAs
+            // it has in flight complete, which serialises S(t+1) and PV(t).  P(t) is complete in TMEM before
+            // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip
+            // was observed, so it cannot read stale data.
             stamp(P.trace, pT, 4);
             if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
             else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
@@ -432,7 +435,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           bool ready = mbar_test(bar_of(bar_k_full, qT), par_of(qT));
           if (ready && q_first) ready = mbar_test(bar_of(bar_q_full, qIq), par_of(qIq));
           if (ready) {
-            tc_fence_after();
             stamp(P.trace, qT, 2);
             const uint32_t tSb = tmem_base + (uint32_t)(qT & 1) * kSStride;
             if (qT & 1) issue_qk<D / 16>(tSb, qd, kd1, idesc_qk);
