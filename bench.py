@@ -50,6 +50,11 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes per launch of the attention kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture, profiles/fwd_sm100_kernel_cfg2.md): measured on the batch-2 cut of cfg2 (534.5 MB) and scaled by
+# the number of work items (x4 for batch 8; per-item statistics are identical).
+TRAFFIC_BYTES = {"cfg2_b2": 534.5e6, "cfg2": 4 * 534.5e6}
+
 # ----------------------------------------------------------------------------------------------
 # synthetic inputs
 # ----------------------------------------------------------------------------------------------
@@ -386,7 +391,7 @@ def ours_arm(args):
                        "l2": "q+k+v+o exceed the 126 MB L2; no flush", "kernel_family": {1: "generic", 2: "sm100"}.get(family, str(family)),
                        "step": "schedule build (3 small kernels) + attention kernel"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "fwd_sm100_kernel" if family == 2 else "fwd_generic_kernel",
+                         "traffic": TRAFFIC_BYTES.get(args.workload), "kernel": "fwd_sm100_kernel" if family == 2 else "fwd_generic_kernel",
                          "kernel_ms": kern_ms, "peak_source": peak_kind},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
