@@ -500,31 +500,45 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
           const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off;
 
-          // ---- this thread's row of S, all in registers
+          // ---- this thread's row of S, all in registers.  The first 16 columns are awaited alone so that
+          //      work on them overlaps the TMEM latency of the rest.
           uint32_t r[64];
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
+          const bool edge = col_limit < my_nc - 1;      // tile on the causal diagonal or at the ragged end of the sample
+          tmem_ld16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
           tmem_wait_ld();
+#pragma unroll
+          for (int j = 1; j < 4; ++j)
+            if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
           if (tid == 0) stamp(P.trace, T, 12);
-          if (col_limit < my_nc - 1) {
-            // tile on the causal diagonal or at the ragged end of the sample: mask in place
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (i > col_limit) r[i] = 0xff800000u;                     // -inf
-          }
 
-          // ---- row maximum
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          bool exact = t == 0;                           // first tile of the item: the maximum must come first
+          if (!exact) {
+            // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
+            // tile's own maximum is computed on the side (any reference gives the same softmax; the
+            // reference only has to keep P in range).  If the tile turns out to exceed the reference by more
+            // than 2^8, the exact pass below redoes it.
+            const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (my_nc > 16 * j) max16(&r[16 * j], mx4);
-          const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
-          if (tid == 0) stamp(P.trace, T, 7);
-          if (t == 0) {
-            m_ref = mx_s;
-          } else {
+            for (int j = 0; j < 4; ++j) {
+              if (my_nc > 16 * j) {
+                if (j == 1) tmem_wait_ld();
+                if (edge) {
+#pragma unroll
+                  for (int i = 16 * j; i < 16 * j + 16; ++i)
+                    if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
+                }
+                uint32_t pk[8];
+                max16(&r[16 * j], mx4);
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                tmem_st8(tSmine + 8 * j, pk);
+              }
+            }
+            if (my_nc <= 16) tmem_wait_ld();
+            const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
             const bool need = mx_s > m_ref + kRescaleThreshold;
+            if (tid == 0) stamp(P.trace, T, 7);
             if (__any_sync(0xffffffffu, need)) {
               // O and l move to the new reference maximum; needs the P V product of the previous tile
               ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
@@ -543,18 +557,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               tmem_wait_st();
               l *= alpha;
               if (need) m_ref = mx_s;
+              exact = true;                              // P of this tile is recomputed against the new reference
+              sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
             }
-          }
-          const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-
-          // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          } else {
+            tmem_wait_ld();
+            if (edge) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (my_nc > 16 * j) {
-              uint32_t pk[8];
-              exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
-              tmem_st8(tSmine + 8 * j, pk);
+              for (int i = 0; i < 64; ++i)
+                if (i > col_limit) r[i] = 0xff800000u;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (my_nc > 16 * j) max16(&r[16 * j], mx4);
+            m_ref = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            if (tid == 0) stamp(P.trace, T, 7);
+          }
+          if (exact) {
+            // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (my_nc > 16 * j) {
+                uint32_t pk[8];
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+                tmem_st8(tSmine + 8 * j, pk);
+              }
             }
           }
           l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
