@@ -146,6 +146,16 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 
 // The same two instructions with the accumulate flag known at compile time (no predicate set-up from
 // a register in the issue loop: the single issuing thread must stay under ~60 clocks per instruction).
+// Register reallocation between the warpgroups of a CTA (executed by every warp of the warpgroup).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 template <bool ACCUMULATE>
 __device__ __forceinline__ void mma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
   if (ACCUMULATE)
