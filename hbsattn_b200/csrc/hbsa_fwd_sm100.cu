@@ -53,8 +53,7 @@ namespace {
 constexpr int kThreads = 320;
 constexpr int kSoftmaxWarps = 4;      // warps 0-3: one thread per row of the M tile
 constexpr int kEpilogueWarps = 4;     // warps 4-7: O / l -> global, off the softmax threads' critical path
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kFirstOtherWarp = 8;     // warps 8 and 9: TMA producer and MMA issuer (which is which depends on the CTA, see the kernel)
 // Register budgets per role (setmaxnreg; 320 threads x 96 registers are allocated at launch).
 constexpr int kRegsSoftmax = 112, kRegsEpilogue = 80, kRegsOther = 96;   // warps 8-9 are a partial warpgroup: they keep the launch value
 static_assert(128 * kRegsSoftmax + 128 * kRegsEpilogue + 64 * kRegsOther <= kThreads * 96, "register budget");
@@ -139,16 +138,18 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[2] = max3(mx[2], __uint_as_float(r[12]), __uint_as_float(r[13]));
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
-// P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
+// P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums
+// (two packed pairs).  The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe
+// time, half the issue slots.
 // (Computing a quarter of the exponentials with a polynomial on the FMA pipe was measured 15-20 % slower.)
 template <bool BF16>
-__device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
+__device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], uint64_t scale2, uint64_t neg_m2, uint64_t (&sum2)[2]) {
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(r[i]), scale_log2, neg_m));
-    const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(r[i + 1]), scale_log2, neg_m));
-    sum[(i >> 1) & 1] += p0;
-    sum[2 + ((i >> 1) & 1)] += p1;
+    float x0, x1;
+    ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2), x0, x1);
+    const float p0 = ptx::ex2_approx(x0), p1 = ptx::ex2_approx(x1);
+    sum2[(i >> 1) & 1] = ptx::add_f32x2(sum2[(i >> 1) & 1], ptx::pack_f32x2(p0, p1));
     pk[i >> 1] = pack2<BF16>(p0, p1);
   }
 }
@@ -243,12 +244,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == kProducerWarp && lane == 0) {
+  // The two CTAs that share an SM (blocks b and b + gridDim.x / 2 of the single wave) put their MMA issuers on
+  // different warp schedulers.
+  const int mma_warp = kFirstOtherWarp + (blockIdx.x < (gridDim.x >> 1) ? 1 : 0);
+  const int producer_warp = kFirstOtherWarp + (kFirstOtherWarp + 1 - mma_warp);
+  if (warp == producer_warp && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
   }
-  if (warp == kMmaWarp) {
+  if (warp == mma_warp) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -260,7 +265,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t kv_tile_bytes = (uint32_t)P.nt * D * 2u;
   const uint32_t kv_panel_bytes = (uint32_t)P.nt * 128u;
 
-  if (warp == kProducerWarp) {
+  if (warp == producer_warp) {
     // =============================== work fetch + TMA producer ===============================
     const ItemRecord* const records = reinterpret_cast<const ItemRecord*>(P.ws.items);
     unsigned long long* const cursor = reinterpret_cast<unsigned long long*>(P.ws.cursor);
@@ -365,7 +370,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_wait_bounded(bar_of(bar_v_full, T - back), par_of(T - back), abort_flag, budget >> 4);
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == mma_warp) {
     // =============================== MMA issuer ===============================
     // One thread issues every tcgen05.mma of the CTA in the order S(0), S(1), PV(0), S(2), PV(1), S(3), ...
     // S(t+2) goes into the buffer that P(t) occupies and is issued right behind PV(t) without waiting for
@@ -498,7 +503,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (tid == 0) stamp(P.trace, T, 12);
 
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          uint64_t sum2[2] = {0ull, 0ull};                // four partial row sums as two fp32 pairs
+          const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2);
           bool exact = t == 0;                           // first tile of the item: the maximum must come first
           if (!exact) {
             // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
@@ -506,6 +512,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // reference only has to keep P in range).  If the tile turns out to exceed the reference by more
             // than 2^8, the exact pass below redoes it.
             const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
+            const uint64_t neg_m02 = ptx::pack_f32x2(neg_m0, neg_m0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (my_nc > 16 * j) {
@@ -517,7 +524,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
                 uint32_t pk[8];
                 max16(&r[16 * j], mx4);
-                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                exp16<BF16>(&r[16 * j], pk, scale2, neg_m02, sum2);
                 tmem_st8(tSmine + 8 * j, pk);
               }
             }
@@ -544,7 +551,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               l *= alpha;
               if (need) m_ref = mx_s;
               exact = true;                              // P of this tile is recomputed against the new reference
-              sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
+              sum2[0] = sum2[1] = 0ull;
             }
           } else {
             tmem_wait_ld();
@@ -562,16 +569,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (exact) {
             // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+            const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (my_nc > 16 * j) {
                 uint32_t pk[8];
-                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+                exp16<BF16>(&r[16 * j], pk, scale2, neg_m2, sum2);
                 tmem_st8(tSmine + 8 * j, pk);
               }
             }
           }
-          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          {
+            float s0, s1;
+            ptx::unpack_f32x2(ptx::add_f32x2(sum2[0], sum2[1]), s0, s1);
+            l += s0 + s1;
+          }
           tmem_wait_st();
           tc_fence_before();
           if (tid == 0) stamp(P.trace, T, 8);
@@ -673,7 +685,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   // ---- teardown: every thread gets here (all waits are bounded)
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == mma_warp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
