@@ -53,7 +53,7 @@ namespace {
 constexpr int kThreads = 320;
 constexpr int kSoftmaxWarps = 4;      // warps 0-3: one thread per row of the M tile
 constexpr int kEpilogueWarps = 4;     // warps 4-7: O / l -> global, off the softmax threads' critical path
-constexpr int kFirstOtherWarp = 8;     // warps 8 and 9: TMA producer and MMA issuer (which is which depends on the CTA, see the kernel)
+constexpr int kFirstOtherWarp = 8;     // warp 8: work fetch + TMA producer, warp 9: MMA issuer
 // Register budgets per role (setmaxnreg; 320 threads x 96 registers are allocated at launch).
 constexpr int kRegsSoftmax = 112, kRegsEpilogue = 80, kRegsOther = 96;   // warps 8-9 are a partial warpgroup: they keep the launch value
 static_assert(128 * kRegsSoftmax + 128 * kRegsEpilogue + 64 * kRegsOther <= kThreads * 96, "register budget");
@@ -83,6 +83,7 @@ struct Sm100Params {
 
 constexpr int kTraceTiles = 96;      // tiles of CTA 0 that are stamped
 constexpr int kTraceSlots = 32;      // stamps per tile
+constexpr int kTraceCtas = 512;      // behind the tile stamps: start time (ns) and SM of the first CTAs
 // slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV(t) issue starts, 5 PV(t) issued,
 // 6 softmax sees S, 7 row max done, 8 P written, 9 P arrival done, 10 item start, 11 epilogue done,
 // 12 S in registers, 13 epilogue starts, 22 last PV seen complete, 23 O in registers
@@ -205,6 +206,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const Problem& p = P.p;
 
   if (P.ws.status[0] != HBSA_STATUS_OK) return;
+  if (P.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceCtas) {
+    unsigned long long ns;
+    uint32_t smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    P.trace[kTraceTiles * kTraceSlots + blockIdx.x] = (long long)ns;
+    P.trace[kTraceTiles * kTraceSlots + kTraceCtas + blockIdx.x] = (long long)smid;
+  }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
@@ -244,10 +253,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
-  // The two CTAs that share an SM (blocks b and b + gridDim.x / 2 of the single wave) put their MMA issuers on
-  // different warp schedulers.
-  const int mma_warp = kFirstOtherWarp + (blockIdx.x < (gridDim.x >> 1) ? 1 : 0);
-  const int producer_warp = kFirstOtherWarp + (kFirstOtherWarp + 1 - mma_warp);
+  constexpr int producer_warp = kFirstOtherWarp, mma_warp = kFirstOtherWarp + 1;
   if (warp == producer_warp && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
@@ -744,7 +750,7 @@ int sm_count() {
 }  // namespace
 
 void sm100_set_trace(long long* device_buffer) { g_trace = device_buffer; }
-size_t sm100_trace_bytes() { return (size_t)kTraceTiles * kTraceSlots * sizeof(long long); }
+size_t sm100_trace_bytes() { return ((size_t)kTraceTiles * kTraceSlots + 2 * kTraceCtas) * sizeof(long long); }
 
 int sm100_kv_tile_rows(int kbs) {
   if (kbs <= kTileRowsMax) return kbs;

@@ -163,7 +163,7 @@ int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
 
 /* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes()
  * bytes is set, the first CTA of every tensor-core attention launch writes clock64() stamps of its
- * pipeline events into it (96 tiles x 32 int64 slots).  NULL switches it off (the default). */
+ * pipeline events into it (96 tiles x 32 int64 slots, then start time and SM of the first 512 CTAs).  NULL switches it off (the default). */
 size_t hbsa_debug_trace_bytes(void);
 void hbsa_debug_set_trace(void* device_buffer);
 
