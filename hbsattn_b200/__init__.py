@@ -12,9 +12,10 @@ _lib_module.load()          # fail loudly at import time when the CUDA library i
 
 from .hbsa_interface import HBSAttention, block_decisions, last_status, set_kernel_family  # noqa: E402
 from .utils import calculate_blocks  # noqa: E402
+from .host_staged import HostStagedAttention  # noqa: E402
 
 __all__ = ["HBSAttention", "calculate_blocks", "block_decisions", "last_status", "set_kernel_family",
-           "install_as_hbsattn"]
+           "HostStagedAttention", "install_as_hbsattn"]
 
 
 def install_as_hbsattn() -> None:
