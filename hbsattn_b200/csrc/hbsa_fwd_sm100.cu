@@ -50,13 +50,10 @@ namespace hbsa {
 
 namespace {
 
-constexpr int kThreads = 320;
-constexpr int kSoftmaxWarps = 4;      // warps 0-3: one thread per row of the M tile
-constexpr int kEpilogueWarps = 4;     // warps 4-7: O / l -> global, off the softmax threads' critical path
-constexpr int kFirstOtherWarp = 8;     // warp 8: work fetch + TMA producer, warp 9: MMA issuer
-// Register budgets per role (setmaxnreg; 320 threads x 96 registers are allocated at launch).
-constexpr int kRegsSoftmax = 112, kRegsEpilogue = 80, kRegsOther = 96;   // warps 8-9 are a partial warpgroup: they keep the launch value
-static_assert(128 * kRegsSoftmax + 128 * kRegsEpilogue + 64 * kRegsOther <= kThreads * 96, "register budget");
+constexpr int kThreads = 192;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
 constexpr int kTileRowsMax = 64;      // rows of a K/V tile
 constexpr int kTmemCols = 256;
 constexpr uint32_t kSStride = 64u;    // TMEM columns between the two S buffers
@@ -110,8 +107,7 @@ struct __align__(16) Control {
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
-  unsigned long long l_full[2];        // [item parity] row sums of an item posted by the softmax warps (count 4)
-  float xl[2][128];                    // [item parity][row] row sum of exponentials, softmax -> epilogue warps
+  uint4 stage[kSoftmaxWarps][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -139,20 +135,25 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[2] = max3(mx[2], __uint_as_float(r[12]), __uint_as_float(r[13]));
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
-// P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums
-// (two packed pairs).  The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe
-// time, half the issue slots.
+// P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
+// The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe time, half the issue
+// slots (measured +6...+11 % on the whole kernel).
 // (Computing a quarter of the exponentials with a polynomial on the FMA pipe was measured 15-20 % slower.)
 template <bool BF16>
-__device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], uint64_t scale2, uint64_t neg_m2, uint64_t (&sum2)[2]) {
+__device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
+  const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2), neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
+  uint64_t sa = ptx::pack_f32x2(sum[0], sum[2]), sb = ptx::pack_f32x2(sum[1], sum[3]);
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
     float x0, x1;
     ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2), x0, x1);
     const float p0 = ptx::ex2_approx(x0), p1 = ptx::ex2_approx(x1);
-    sum2[(i >> 1) & 1] = ptx::add_f32x2(sum2[(i >> 1) & 1], ptx::pack_f32x2(p0, p1));
+    if ((i >> 1) & 1) sb = ptx::add_f32x2(sb, ptx::pack_f32x2(p0, p1));
+    else sa = ptx::add_f32x2(sa, ptx::pack_f32x2(p0, p1));
     pk[i >> 1] = pack2<BF16>(p0, p1);
   }
+  ptx::unpack_f32x2(sa, sum[0], sum[2]);
+  ptx::unpack_f32x2(sb, sum[1], sum[3]);
 }
 
 // One lane polls the mbarrier, the rest of the warp sleeps at the shuffle instead of spinning.
@@ -165,33 +166,28 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ uint32_t bar_of(uint32_t base, int c) { return base + 8u * (uint32_t)(c & 1); }
 __device__ __forceinline__ uint32_t par_of(int c) { return (uint32_t)(c >> 1) & 1u; }
 
-// The issue sequences of the MMA thread.  A descriptor is the low word of the tile's first descriptor plus
-// a compile-time offset (16 head dims further = 2 units inside a 64-dim panel of Q or K; 16 keys further =
-// 128 units of V and 8 TMEM columns of P), so a product is little more than back-to-back tcgen05.mma.
+// The issue sequences of the MMA thread.  Every descriptor and TMEM address is precomputed into
+// registers once per CTA, so a product is nothing but back-to-back tcgen05.mma instructions.
 template <int KSTEPS>
-__device__ __forceinline__ void issue_qk(uint32_t tS, uint32_t q_lo, uint32_t k_lo, uint32_t kpanel_units, uint32_t hi, uint32_t idesc) {
+__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[8], const uint64_t (&kd)[8], uint32_t idesc) {
+  ptx::mma_ss_c<false>(tS, qd[0], kd[0], idesc);
 #pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
-    const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
-    if (ks == 0) ptx::mma_ss_c<false>(tS, ptx::smem_desc_join(q_lo + qo, hi), ptx::smem_desc_join(k_lo + ko, hi), idesc);
-    else ptx::mma_ss_c<true>(tS, ptx::smem_desc_join(q_lo + qo, hi), ptx::smem_desc_join(k_lo + ko, hi), idesc);
-  }
+  for (int ks = 1; ks < KSTEPS; ++ks) ptx::mma_ss_c<true>(tS, qd[ks], kd[ks], idesc);
 }
 // N k-steps of O (+)= P V; the first one overwrites O when `first`.
 template <int N>
-__device__ __forceinline__ void issue_pv_n(uint32_t tO, uint32_t p_addr, uint32_t v_lo, uint32_t hi, uint32_t idesc, bool first) {
-  if (first) ptx::mma_ts_c<false>(tO, p_addr, ptx::smem_desc_join(v_lo, hi), idesc);
-  else ptx::mma_ts_c<true>(tO, p_addr, ptx::smem_desc_join(v_lo, hi), idesc);
+__device__ __forceinline__ void issue_pv_n(uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
+  if (first) ptx::mma_ts_c<false>(tO, pa[0], vd[0], idesc);
+  else ptx::mma_ts_c<true>(tO, pa[0], vd[0], idesc);
 #pragma unroll
-  for (int ks = 1; ks < N; ++ks) ptx::mma_ts_c<true>(tO, p_addr + 8u * ks, ptx::smem_desc_join(v_lo + 128u * ks, hi), idesc);
+  for (int ks = 1; ks < N; ++ks) ptx::mma_ts_c<true>(tO, pa[ks], vd[ks], idesc);
 }
-__device__ __forceinline__ void issue_pv(int n, uint32_t tO, uint32_t p_addr, uint32_t v_lo, uint32_t hi, uint32_t idesc, bool first) {
+__device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
   switch (n) {
-    case 1: issue_pv_n<1>(tO, p_addr, v_lo, hi, idesc, first); break;
-    case 2: issue_pv_n<2>(tO, p_addr, v_lo, hi, idesc, first); break;
-    case 3: issue_pv_n<3>(tO, p_addr, v_lo, hi, idesc, first); break;
-    default: issue_pv_n<4>(tO, p_addr, v_lo, hi, idesc, first); break;
+    case 1: issue_pv_n<1>(tO, pa, vd, idesc, first); break;
+    case 2: issue_pv_n<2>(tO, pa, vd, idesc, first); break;
+    case 3: issue_pv_n<3>(tO, pa, vd, idesc, first); break;
+    default: issue_pv_n<4>(tO, pa, vd, idesc, first); break;
   }
 }
 
@@ -232,7 +228,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
   const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
   const uint32_t bar_p_full = smem_u32(&ctl->p_full[0]), bar_pv_done = smem_u32(&ctl->pv_done[0]);
-  const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]), bar_l_full = smem_u32(&ctl->l_full[0]);
+  const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]);
   volatile int* const abort_flag = &ctl->abort_flag;
   volatile int* const tile_k0 = ctl->tile_k0;
   volatile ItemSlot* const slots = ctl->slot;
@@ -240,26 +236,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_item_full + 8 * i, 1);
-      mbar_init(bar_item_done + 8 * i, kSoftmaxWarps + kEpilogueWarps + 1);      // softmax and epilogue warps + the MMA thread
+      mbar_init(bar_item_done + 8 * i, kSoftmaxWarps + 1);      // softmax warps + the MMA thread
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_k_full + 8 * i, 1);
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
       mbar_init(bar_p_full + 8 * i, kSoftmaxWarps);
       mbar_init(bar_pv_done + 8 * i, 1);
-      mbar_init(bar_o_free + 8 * i, kEpilogueWarps);
-      mbar_init(bar_l_full + 8 * i, kSoftmaxWarps);
+      mbar_init(bar_o_free + 8 * i, kSoftmaxWarps);
     }
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
-  constexpr int producer_warp = kFirstOtherWarp, mma_warp = kFirstOtherWarp + 1;
-  if (warp == producer_warp && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
   }
-  if (warp == mma_warp) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tmem_relinquish();
   }
@@ -271,7 +265,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t kv_tile_bytes = (uint32_t)P.nt * D * 2u;
   const uint32_t kv_panel_bytes = (uint32_t)P.nt * 128u;
 
-  if (warp == producer_warp) {
+  if (warp == kProducerWarp) {
     // =============================== work fetch + TMA producer ===============================
     const ItemRecord* const records = reinterpret_cast<const ItemRecord*>(P.ws.items);
     unsigned long long* const cursor = reinterpret_cast<unsigned long long*>(P.ws.cursor);
@@ -376,7 +370,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_wait_bounded(bar_of(bar_v_full, T - back), par_of(T - back), abort_flag, budget >> 4);
       }
     }
-  } else if (warp == mma_warp) {
+  } else if (warp == kMmaWarp) {
     // =============================== MMA issuer ===============================
     // One thread issues every tcgen05.mma of the CTA in the order S(0), S(1), PV(0), S(2), PV(1), S(3), ...
     // S(t+2) goes into the buffer that P(t) occupies and is issued right behind PV(t) without waiting for
@@ -389,9 +383,25 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int ksteps = P.nt >> 4;
       const uint32_t desc_hi = smem_desc_hi(1024u);
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
-      const uint32_t q_lo = smem_desc_lo(sQ, 16u);
-      const uint32_t k_lo0 = smem_desc_lo(sK, 16u), k_lo1 = smem_desc_lo(sK + KV_BYTES_MAX, 16u);
-      const uint32_t v_lo0 = smem_desc_lo(sV, kv_panel_bytes), v_lo1 = smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes);
+      // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
+      // V is MN-major: 16 keys further = 2048 bytes = 128 units.  P: 8 TMEM columns per 16 keys.
+      uint64_t qd[8], kd0[8], kd1[8], vd0[4], vd1[4];
+      uint32_t pa0[4], pa1[4];
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
+        const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
+        qd[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
+        kd0[ks] = smem_desc_join(smem_desc_lo(sK, 16u) + ko, desc_hi);
+        kd1[ks] = smem_desc_join(smem_desc_lo(sK + KV_BYTES_MAX, 16u) + ko, desc_hi);
+      }
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        vd0[ks] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        vd1[ks] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        pa0[ks] = tmem_base + (uint32_t)ks * 8u;
+        pa1[ks] = tmem_base + kSStride + (uint32_t)ks * 8u;
+      }
       const uint32_t tO = tmem_base + kTmemOCol;
       // S side: item qI (count of published items), its tiles left, number of items with tiles so far, next tile
       int qI = 0, q_left = 0, qIq = 0, qT = 0;
@@ -427,8 +437,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip
             // was observed, so it cannot read stale data.
             stamp(P.trace, pT, 4);
-            issue_pv(ksteps, tO, tmem_base + (uint32_t)(pT & 1) * kSStride, (pT & 1) ? v_lo1 : v_lo0, desc_hi, idesc_pv,
-                     fl_first[pT & 1] != 0);
+            if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
+            else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
             tc_commit(bar_of(bar_pv_done, pT));
             stamp(P.trace, pT, 5);
             if (fl_first[pT & 1]) ++pIq;
@@ -443,7 +453,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (ready) {
             stamp(P.trace, qT, 2);
             const uint32_t tSb = tmem_base + (uint32_t)(qT & 1) * kSStride;
-            issue_qk<D / 16>(tSb, q_lo, (qT & 1) ? k_lo1 : k_lo0, kpanel_units, desc_hi, idesc_qk);
+            if (qT & 1) issue_qk<D / 16>(tSb, qd, kd1, idesc_qk);
+            else issue_qk<D / 16>(tSb, qd, kd0, idesc_qk);
             tc_commit(bar_of(bar_s_full, qT));
             stamp(P.trace, qT, 3);
             fl_first[qT & 1] = q_first ? 1 : 0;
@@ -469,9 +480,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
     __syncwarp();
-  } else if (warp < kSoftmaxWarps) {
-    // =============================== softmax ===============================
-    setmaxnreg_inc<kRegsSoftmax>();
+  } else {
+    // =============================== softmax + epilogue ===============================
     const int row = tid;                             // 0..127: row of the M tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const int my_nc = P.nt;                          // columns of a tile: 16, 32, 48 or 64
@@ -484,7 +494,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!ok) break;
       const int n_tiles = slots[I & 1].n_tiles;
       if (n_tiles < 0) break;
-      if (n_tiles > 0) {
+      const int tile_tok0 = slots[I & 1].tile_tok0, head0 = slots[I & 1].head0, q_end = slots[I & 1].q_end;
+      if (n_tiles == 0) {
+        // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
+        const int r_tok = tile_tok0 + (row >> P.gp_shift);
+        if (r_tok < q_end) {
+          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+        }
+      } else {
         int limit_row = slots[I & 1].k_len - 1;
         if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
@@ -509,8 +528,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (tid == 0) stamp(P.trace, T, 12);
 
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-          uint64_t sum2[2] = {0ull, 0ull};                // four partial row sums as two fp32 pairs
-          const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2);
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
           bool exact = t == 0;                           // first tile of the item: the maximum must come first
           if (!exact) {
             // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
@@ -518,7 +536,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // reference only has to keep P in range).  If the tile turns out to exceed the reference by more
             // than 2^8, the exact pass below redoes it.
             const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
-            const uint64_t neg_m02 = ptx::pack_f32x2(neg_m0, neg_m0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (my_nc > 16 * j) {
@@ -530,7 +547,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
                 uint32_t pk[8];
                 max16(&r[16 * j], mx4);
-                exp16<BF16>(&r[16 * j], pk, scale2, neg_m02, sum2);
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
                 tmem_st8(tSmine + 8 * j, pk);
               }
             }
@@ -557,7 +574,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               l *= alpha;
               if (need) m_ref = mx_s;
               exact = true;                              // P of this tile is recomputed against the new reference
-              sum2[0] = sum2[1] = 0ull;
+              sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
             }
           } else {
             tmem_wait_ld();
@@ -575,21 +592,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (exact) {
             // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
             const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-            const uint64_t neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (my_nc > 16 * j) {
                 uint32_t pk[8];
-                exp16<BF16>(&r[16 * j], pk, scale2, neg_m2, sum2);
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
                 tmem_st8(tSmine + 8 * j, pk);
               }
             }
           }
-          {
-            float s0, s1;
-            ptx::unpack_f32x2(ptx::add_f32x2(sum2[0], sum2[1]), s0, s1);
-            l += s0 + s1;
-          }
+          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
           tmem_wait_st();
           tc_fence_before();
           if (tid == 0) stamp(P.trace, T, 8);
@@ -598,88 +610,55 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (tid == 0) stamp(P.trace, T, 9);
         }
         if (!ok) break;
-        // ---- hand the row sums to the epilogue warps and go on with the next item.  The slot is free
-        //      once the epilogue of the item two back has read it (it reads before it releases O).
-        if (Iq >= 2) {
-          ok = warp_wait(bar_of(bar_o_free, Iq - 2), par_of(Iq - 2), abort_flag, budget);
-          if (!ok) break;
-        }
-        ctl->xl[Iq & 1][row] = l;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_of(bar_l_full, Iq));
+
+        // ---- epilogue: O / l -> global; rows past the q-block end are dropped, rows that saw no key are zeros
         if (tid == 0) stamp(P.trace, T - 1, 13);
-        ++Iq;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_of(bar_item_done, I));
-      ++I;
-    }
-  } else if (warp < kSoftmaxWarps + kEpilogueWarps) {
-    // =============================== epilogue ===============================
-    // O / l -> global; rows past the q-block end are dropped, rows that saw no key are zeros.
-    setmaxnreg_dec<kRegsEpilogue>();
-    const int ew = warp - kSoftmaxWarps;             // TMEM lane quarter (= warp % 4)
-    const int row = ew * 32 + lane;
-    const uint32_t tOmine = tmem_base + kTmemOCol + ((uint32_t)(ew * 32) << 16);
-    int I = 0, Iq = 0, T = 0;                        // T: tiles of all items so far
-    bool ok = true;
-    while (ok) {
-      ok = warp_wait(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
-      if (!ok) break;
-      const int n_tiles = slots[I & 1].n_tiles;
-      if (n_tiles < 0) break;
-      const int tile_tok0 = slots[I & 1].tile_tok0, head0 = slots[I & 1].head0, q_end = slots[I & 1].q_end;
-      if (n_tiles == 0) {
-        // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
-        const int r_tok = tile_tok0 + (row >> P.gp_shift);
-        if (r_tok < q_end) {
-          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
-#pragma unroll
-          for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
-        }
-      } else {
-        T += n_tiles;
-        const int r_tok = tile_tok0 + (row >> P.gp_shift);
-        const bool r_valid = r_tok < q_end;
-        OutT* const orow = o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1;
-        ok = warp_wait(bar_of(bar_l_full, Iq), par_of(Iq), abort_flag, budget);
-        if (!ok) break;
-        const float l = *reinterpret_cast<volatile float*>(&ctl->xl[Iq & 1][row]);
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        const uint32_t keep = l > 0.f ? 0xffffffffu : 0u;                    // rows that saw no key are exact zeros
+        const bool live = l > 0.f;
+        const float inv = live ? 1.f / l : 0.f;
         ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
-        if (warp == kSoftmaxWarps && lane == 0) stamp(P.trace, T - 1, 22);
-        // Drain O 64 columns per TMEM round trip (the load latency, not the bandwidth, is what costs);
-        // each thread writes 128 contiguous bytes of its row per trip.
+        if (tid == 0) stamp(P.trace, T - 1, 22);
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 64) {
-          uint32_t oa[2][32];
-          tmem_ld32(tOmine + c0, oa[0]);
-          tmem_ld32(tOmine + c0 + 32, oa[1]);
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t oa[32];
+          tmem_ld32(tOmine + c0, oa);
           tmem_wait_ld();
-          if (c0 + 64 >= D) {
+          if (c0 + 32 >= D) {
             tc_fence_before();                                             // O is in registers: the next item may overwrite it
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
-            if (warp == kSoftmaxWarps && lane == 0) stamp(P.trace, T - 1, 23);
+            if (tid == 0) stamp(P.trace, T - 1, 23);
           }
+          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
+          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
+          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
+          uint4* const st = &ctl->stage[warp][0][0];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t w[4];
+            for (int j = 0; j < 4; ++j) {
+              const int e = i * 8 + j * 2;
+              w[j] = live ? pack2<BF16>(__uint_as_float(oa[e]) * inv, __uint_as_float(oa[e + 1]) * inv) : 0u;
+            }
+            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          __syncwarp();
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int e = i * 8 + j * 2;
-                w[j] = pack2<BF16>(__uint_as_float(oa[h][e]) * inv, __uint_as_float(oa[h][e + 1]) * inv) & keep;
-              }
-              if (r_valid) *reinterpret_cast<uint4*>(orow + c0 + h * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int i = 0; i < 4; ++i) {
+            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
+            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
+            const int rg = warp * 32 + rr;                                  // row of the M tile
+            const int tok = tile_tok0 + (rg >> P.gp_shift);
+            if (tok < q_end) {
+              OutT* dst = o_base + tok * P.o_s0 + (head0 + (rg & (P.gp - 1))) * P.o_s1 + c0 + cc * 8;
+              *reinterpret_cast<uint4*>(dst) = val;
             }
           }
+          __syncwarp();
         }
-        if (warp == kSoftmaxWarps && lane == 0) stamp(P.trace, T - 1, 11);
+        if (tid == 0) stamp(P.trace, T - 1, 11);
         ++Iq;
       }
       __syncwarp();
@@ -691,7 +670,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   // ---- teardown: every thread gets here (all waits are bounded)
   tc_fence_before();
   __syncthreads();
-  if (warp == mma_warp) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
