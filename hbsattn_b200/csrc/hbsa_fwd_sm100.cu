@@ -615,6 +615,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (tid == 0) stamp(P.trace, T - 1, 13);
         const bool live = l > 0.f;
         const float inv = live ? 1.f / l : 0.f;
+        const uint64_t inv2 = pack_f32x2(inv, inv);
         ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
@@ -640,7 +641,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int e = i * 8 + j * 2;
-              w[j] = live ? pack2<BF16>(__uint_as_float(oa[e]) * inv, __uint_as_float(oa[e + 1]) * inv) : 0u;
+              float y0, y1;
+              unpack_f32x2(mul_f32x2(pack_b32x2(oa[e], oa[e + 1]), inv2), y0, y1);
+              w[j] = live ? pack2<BF16>(y0, y1) : 0u;
             }
             st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
           }
