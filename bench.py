@@ -218,6 +218,11 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use the host cores it can get
+    try:
+        torch.set_num_threads(max(torch.get_num_threads(), min(len(os.sched_getaffinity(0)), 64)))
+    except (AttributeError, OSError):
+        pass
     wl = make_workload(args.workload, 0, "cpu")
     w = wl["w"]
     cores = torch.get_num_threads()
