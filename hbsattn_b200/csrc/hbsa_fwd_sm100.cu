@@ -191,7 +191,9 @@ __device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa
   }
 }
 
-template <int D, bool BF16>
+// TRACE = true is the instantiation that runs while a debug trace buffer is set; the shipped path carries
+// no stamp code at all (the checks alone were a tenth of the softmax threads' instructions).
+template <int D, bool BF16, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 2)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
@@ -202,7 +204,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const Problem& p = P.p;
 
   if (P.ws.status[0] != HBSA_STATUS_OK) return;
-  if (P.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceCtas) {
+  if (TRACE && P.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceCtas) {
     unsigned long long ns;
     uint32_t smid;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
@@ -346,7 +348,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
               for (int pn = 0; pn < PANELS; ++pn)
                 tma_load_3d(sK + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_k, bar_of(bar_k_full, T), pn * 64, rec.hk, rec.k_begin + k0);
-              stamp(P.trace, T, 0);
+              if (TRACE) stamp(P.trace, T, 0);
             }
             // V stage T & 1 is free once the P V product of tile T-2 is done
             if (T >= 2) ok = warp_wait(bar_of(bar_pv_done, T), par_of(T - 2), abort_flag, budget);
@@ -356,7 +358,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
               for (int pn = 0; pn < PANELS; ++pn)
                 tma_load_3d(sV + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_v, bar_of(bar_v_full, T), pn * 64, rec.hk, rec.k_begin + k0);
-              stamp(P.trace, T, 1);
+              if (TRACE) stamp(P.trace, T, 1);
             }
             ++T;
           }
@@ -436,11 +438,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // it has in flight complete, which serialises S(t+1) and PV(t).  P(t) is complete in TMEM before
             // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip
             // was observed, so it cannot read stale data.
-            stamp(P.trace, pT, 4);
+            if (TRACE) stamp(P.trace, pT, 4);
             if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
             else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
             tc_commit(bar_of(bar_pv_done, pT));
-            stamp(P.trace, pT, 5);
+            if (TRACE) stamp(P.trace, pT, 5);
             if (fl_first[pT & 1]) ++pIq;
             if (fl_last[pT & 1]) mbar_arrive(bar_of(bar_item_done, fl_item[pT & 1]));   // through with the item
             ++pT;
@@ -451,12 +453,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           bool ready = mbar_test(bar_of(bar_k_full, qT), par_of(qT));
           if (ready && q_first) ready = mbar_test(bar_of(bar_q_full, qIq), par_of(qIq));
           if (ready) {
-            stamp(P.trace, qT, 2);
+            if (TRACE) stamp(P.trace, qT, 2);
             const uint32_t tSb = tmem_base + (uint32_t)(qT & 1) * kSStride;
             if (qT & 1) issue_qk<D / 16>(tSb, qd, kd1, idesc_qk);
             else issue_qk<D / 16>(tSb, qd, kd0, idesc_qk);
             tc_commit(bar_of(bar_s_full, qT));
-            stamp(P.trace, qT, 3);
+            if (TRACE) stamp(P.trace, qT, 3);
             fl_first[qT & 1] = q_first ? 1 : 0;
             fl_last[qT & 1] = q_left == 1 ? 1 : 0;
             fl_item[qT & 1] = qI;
@@ -507,12 +509,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         int limit_row = slots[I & 1].k_len - 1;
         if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
-        if (tid == 0) stamp(P.trace, T, 10);
+        if (TRACE && tid == 0) stamp(P.trace, T, 10);
         for (int t = 0; t < n_tiles && ok; ++t, ++T) {
           ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
           if (!ok) break;
           tc_fence_after();
-          if (tid == 0) stamp(P.trace, T, 6);
+          if (TRACE && tid == 0) stamp(P.trace, T, 6);
           const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
           const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off;
 
@@ -525,7 +527,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int j = 1; j < 4; ++j)
             if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
-          if (tid == 0) stamp(P.trace, T, 12);
+          if (TRACE && tid == 0) stamp(P.trace, T, 12);
 
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           float sum[4] = {0.f, 0.f, 0.f, 0.f};
@@ -554,7 +556,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (my_nc <= 16) tmem_wait_ld();
             const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
             const bool need = mx_s > m_ref + kRescaleThreshold;
-            if (tid == 0) stamp(P.trace, T, 7);
+            if (TRACE && tid == 0) stamp(P.trace, T, 7);
             if (__any_sync(0xffffffffu, need)) {
               // O and l move to the new reference maximum; needs the P V product of the previous tile
               ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
@@ -587,7 +589,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int j = 0; j < 4; ++j)
               if (my_nc > 16 * j) max16(&r[16 * j], mx4);
             m_ref = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            if (tid == 0) stamp(P.trace, T, 7);
+            if (TRACE && tid == 0) stamp(P.trace, T, 7);
           }
           if (exact) {
             // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
@@ -604,22 +606,22 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
           tmem_wait_st();
           tc_fence_before();
-          if (tid == 0) stamp(P.trace, T, 8);
+          if (TRACE && tid == 0) stamp(P.trace, T, 8);
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
-          if (tid == 0) stamp(P.trace, T, 9);
+          if (TRACE && tid == 0) stamp(P.trace, T, 9);
         }
         if (!ok) break;
 
         // ---- epilogue: O / l -> global; rows past the q-block end are dropped, rows that saw no key are zeros
-        if (tid == 0) stamp(P.trace, T - 1, 13);
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 13);
         const bool live = l > 0.f;
         const float inv = live ? 1.f / l : 0.f;
         const uint64_t inv2 = pack_f32x2(inv, inv);
         ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
-        if (tid == 0) stamp(P.trace, T - 1, 22);
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 22);
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t oa[32];
@@ -629,7 +631,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tc_fence_before();                                             // O is in registers: the next item may overwrite it
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
-            if (tid == 0) stamp(P.trace, T - 1, 23);
+            if (TRACE && tid == 0) stamp(P.trace, T - 1, 23);
           }
           // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
           // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
@@ -661,7 +663,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
           __syncwarp();
         }
-        if (tid == 0) stamp(P.trace, T - 1, 11);
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 11);
         ++Iq;
       }
       __syncwarp();
@@ -799,16 +801,18 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
 
   const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
-#define HBSA_LAUNCH_SM100(D_, BF_)                                                                        \
+#define HBSA_LAUNCH_SM100(D_, BF_, TR_)                                                                   \
   do {                                                                                                   \
-    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, TR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) {                                                                              \
-      fwd_sm100_kernel<D_, BF_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                        \
+      fwd_sm100_kernel<D_, BF_, TR_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                   \
       e = cudaGetLastError();                                                                            \
     }                                                                                                    \
   } while (0)
-  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100(128, true); else HBSA_LAUNCH_SM100(128, false); }
-  else { if (bf16) HBSA_LAUNCH_SM100(64, true); else HBSA_LAUNCH_SM100(64, false); }
+#define HBSA_LAUNCH_SM100_T(D_, BF_) do { if (P.trace != nullptr) HBSA_LAUNCH_SM100(D_, BF_, true); else HBSA_LAUNCH_SM100(D_, BF_, false); } while (0)
+  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
+  else { if (bf16) HBSA_LAUNCH_SM100_T(64, true); else HBSA_LAUNCH_SM100_T(64, false); }
+#undef HBSA_LAUNCH_SM100_T
 #undef HBSA_LAUNCH_SM100
   if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return (int)e; }
   return 0;
