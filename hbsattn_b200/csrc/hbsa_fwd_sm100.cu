@@ -683,6 +683,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     atomicExch(&P.ws.status[0], HBSA_STATUS_WAIT_LIMIT);
     P.ws.status[3] = (int)blockIdx.x;
   }
+  // The last CTA to leave rewinds the work cursor, so that the same schedule can drive the next launch
+  // (every CTA is past its last fetch by the time it gets here).  Word 2 of the cursor block counts the leavers.
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(reinterpret_cast<unsigned int*>(P.ws.cursor) + 2, 1u) == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned long long*>(P.ws.cursor) = 0ull;
+      reinterpret_cast<volatile unsigned int*>(P.ws.cursor)[2] = 0u;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------ host

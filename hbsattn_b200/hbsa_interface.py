@@ -188,3 +188,62 @@ def block_decisions(q, k, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, 
             raise RuntimeError(f"hbsa_block_decisions failed ({rc}): {_lib.last_error()}")
         _state["last_workspace"] = ws
     return dec.bool(), counts
+
+
+class MaskSchedule:
+    """The work schedule of one (cu_q_seqlens, cu_k_seqlens, block_mask, block sizes, causal) layout, built once
+    on the device by ``build_schedule`` and reused by ``attention_with_schedule`` for every call that shares the
+    layout (the layers of a model, the steps of a decode loop).  The reference's callers reuse the outputs of
+    ``calculate_blocks`` the same way (``test/test_speedup.py:100-102,152``); here the reusable part also holds the
+    active k-block counts and the ordered work-item table, so a reused call launches the attention kernel alone.
+
+    The tensors the schedule was built from must stay alive and unchanged while it is in use, and calls that share
+    a schedule must not overlap on the GPU (the kernel's work cursor lives in the schedule)."""
+
+    def __init__(self, workspace, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal):
+        self.workspace = workspace
+        self.cu_q_seqlens, self.cu_k_seqlens, self.block_mask = cu_q32, cu_k32, block_mask
+        self.q_block_size, self.k_block_size, self.causal = int(q_block_size), int(k_block_size), bool(causal)
+        self.nhead_k, self.num_q_block, self.num_k_block = block_mask.shape
+
+
+def build_schedule(q, k, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal) -> MaskSchedule:
+    """``q`` and ``k`` only say which shapes, dtype and device the later calls will have; they are not read."""
+    assert block_mask.dtype == torch.bool and block_mask.ndim == 3, "block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block)"
+    assert block_mask.shape[0] == k.shape[1], f"block_mask must have nheads_k = {k.shape[1]} planes"
+    assert q_block_size % 16 == 0 and k_block_size % 16 == 0 and q_block_size > 0 and k_block_size > 0, \
+        "q_block_size and k_block_size must be integer multiples of 16."
+    cu_q32, cu_k32 = _prepare(q, k, k, cu_q_seqlens, cu_k_seqlens, block_mask)
+    lib = _lib.load()
+    dev = q.device
+    nhk, nqb, nkb = block_mask.shape
+    with torch.cuda.device(dev):
+        ws = alloc_workspace(nhk, nqb, nkb, cu_q32.numel() - 1, dev)
+        args = make_args(q, k, k, None, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, None, nqb, nkb, ws,
+                         _IMPLS[_state["impl"]])
+        rc = lib.hbsa_build_schedule(ctypes.byref(args), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_build_schedule failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+    return MaskSchedule(ws, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal)
+
+
+def attention_with_schedule(q, k, v, schedule: MaskSchedule, softmax_scale=None):
+    """``HBSAttention`` for a layout whose schedule is already on the device: one kernel launch."""
+    assert q.shape[1] % k.shape[1] == 0, "nhead_q must be divisible by nhead_k (for GQA)"
+    assert k.shape[1] == schedule.nhead_k, "k has a different number of heads than the schedule's block_mask"
+    s = schedule
+    _prepare(q, k, v, s.cu_q_seqlens, s.cu_k_seqlens, s.block_mask)
+    lib = _lib.load()
+    dev = q.device
+    with torch.cuda.device(dev):
+        out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        if q.shape[0] == 0:
+            return out
+        args = make_args(q, k, v, out, s.cu_q_seqlens, s.cu_k_seqlens, s.block_mask, s.q_block_size, s.k_block_size, s.causal,
+                         softmax_scale, s.num_q_block, s.num_k_block, s.workspace, _IMPLS[_state["impl"]])
+        rc = lib.hbsa_attention(ctypes.byref(args), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_attention failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = s.workspace
+    return out

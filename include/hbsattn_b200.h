@@ -137,7 +137,9 @@ int hbsa_forward(const hbsa_forward_args* args, void* stream);
  *       (kv-head, q-block) row, rows ordered by descending work - all into `workspace`
  *       (q, k, v, o are not read and may be NULL).
  *   hbsa_attention: the attention kernel alone; `workspace` must hold the schedule built from the
- *       same cu_*_seqlens, block_mask, block sizes and causal flag.
+ *       same cu_*_seqlens, block_mask, block sizes and causal flag.  A schedule serves any number
+ *       of launches (the kernel rewinds its work cursor when it finishes); launches that share a
+ *       schedule must not overlap on the GPU.
  */
 int hbsa_build_schedule(const hbsa_forward_args* args, void* stream);
 int hbsa_attention(const hbsa_forward_args* args, void* stream);
