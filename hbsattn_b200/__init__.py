@@ -10,13 +10,13 @@ from . import _lib as _lib_module
 
 _lib_module.load()          # fail loudly at import time when the CUDA library is missing
 
-from .hbsa_interface import (HBSAttention, MaskSchedule, attention_with_schedule, block_decisions,  # noqa: E402
+from .hbsa_interface import (HBSAttention, HBSAttention_with_lse, MaskSchedule, attention_with_schedule, block_decisions,  # noqa: E402
                              build_schedule, last_status, set_kernel_family)
 from .utils import calculate_blocks  # noqa: E402
 from .host_staged import HostStagedAttention  # noqa: E402
 
 __all__ = ["HBSAttention", "calculate_blocks", "block_decisions", "last_status", "set_kernel_family",
-           "HostStagedAttention", "MaskSchedule", "build_schedule", "attention_with_schedule", "install_as_hbsattn"]
+           "HBSAttention_with_lse", "HostStagedAttention", "MaskSchedule", "build_schedule", "attention_with_schedule", "install_as_hbsattn"]
 
 
 def install_as_hbsattn() -> None:

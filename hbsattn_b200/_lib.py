@@ -70,6 +70,7 @@ class ForwardArgs(ctypes.Structure):
         ("reserved", ctypes.c_int32),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("lse", ctypes.c_void_p),
     ]
 
 
@@ -115,7 +116,7 @@ def load() -> ctypes.CDLL:
         lib.hbsa_debug_trace_bytes.argtypes = []
         lib.hbsa_debug_set_trace.restype = None
         lib.hbsa_debug_set_trace.argtypes = [vp]
-        if lib.hbsa_version() != 1:
+        if lib.hbsa_version() != 2:
             raise ImportError("libhbsattn_b200.so was built from a different ABI version")
         _lib = lib
         return lib

@@ -28,7 +28,7 @@ constexpr int kRowsPerCta = 32;
 template <typename T, int DQ, int KT>
 __global__ void __launch_bounds__(128)
 fwd_generic_kernel(Problem p, Workspace ws, const T* __restrict__ q, const T* __restrict__ k,
-                   const T* __restrict__ v, T* __restrict__ o, Strides st, int chunks_per_block) {
+                   const T* __restrict__ v, T* __restrict__ o, float* __restrict__ lse, Strides st, int chunks_per_block) {
   constexpr int DPAD = DQ * 4;
   if (ws.status[0] != HBSA_STATUS_OK) return;
   extern __shared__ float smem[];
@@ -123,6 +123,8 @@ fwd_generic_kernel(Problem p, Workspace ws, const T* __restrict__ q, const T* __
       const int d = sub + 4 * i;
       if (d < p.headdim) store_f(o + tok * st.o0 + hq * st.o1 + d * st.o2, acc[i] * inv);
     }
+    // scores are kept in the log2 domain: ln sum exp = ln 2 * (m + log2 l)
+    if (lse != nullptr && sub == 0) lse[(long long)tok * p.nhead_q + hq] = l > 0.f ? 0.6931471805599453f * (m + log2f(l)) : -INFINITY;
   }
 }
 
@@ -137,7 +139,7 @@ static cudaError_t launch_typed(const Problem& p, const Workspace& ws, const hbs
   const T* v = static_cast<const T*>(a.v);
   T* o = static_cast<T*>(a.o);
 #define HBSA_LAUNCH_GENERIC(DQ_, KT_)                                                                   \
-  fwd_generic_kernel<T, DQ_, KT_><<<grid, 128, 2 * KT_ * DQ_ * 4 * sizeof(float), stream>>>(p, ws, q, k, v, o, st, cpb)
+  fwd_generic_kernel<T, DQ_, KT_><<<grid, 128, 2 * KT_ * DQ_ * 4 * sizeof(float), stream>>>(p, ws, q, k, v, o, a.lse, st, cpb)
   if (p.headdim <= 32) HBSA_LAUNCH_GENERIC(8, 32);
   else if (p.headdim <= 64) HBSA_LAUNCH_GENERIC(16, 32);
   else if (p.headdim <= 128) HBSA_LAUNCH_GENERIC(32, 32);

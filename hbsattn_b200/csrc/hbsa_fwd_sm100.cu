@@ -65,6 +65,7 @@ struct Sm100Params {
   Workspace ws;
   void* o;
   long long o_s0, o_s1;        // elements
+  float* lse;                  // NULL or [total_q, nhead_q]: natural-log sum of exponentials per row
   int nt;                      // rows of one K/V tile (multiple of 16, <= 64)
   int n_sub;                   // K/V tiles per k-block
   int gp, gp_shift;            // q-heads packed into one M tile
@@ -504,6 +505,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
 #pragma unroll
           for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          if (P.lse != nullptr) P.lse[(long long)r_tok * p.nhead_q + head0 + (row & (P.gp - 1))] = -INFINITY;
         }
       } else {
         int limit_row = slots[I & 1].k_len - 1;
@@ -618,6 +620,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const bool live = l > 0.f;
         const float inv = live ? 1.f / l : 0.f;
         const uint64_t inv2 = pack_f32x2(inv, inv);
+        if (P.lse != nullptr) {
+          // ln sum exp of the row's scaled scores = ln 2 * (reference + log2 l), whatever reference was used
+          const int r_tok = tile_tok0 + (tid >> P.gp_shift);
+          if (r_tok < q_end)
+            P.lse[(long long)r_tok * p.nhead_q + head0 + (tid & (P.gp - 1))] = live ? 0.6931471805599453f * (m_ref + log2f(l)) : -INFINITY;
+        }
         ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
@@ -778,6 +786,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.p = p;
   P.ws = ws;
   P.o = a.o;
+  P.lse = a.lse;
   P.o_s0 = a.o_stride[0];
   P.o_s1 = a.o_stride[1];
   P.nt = sm100_kv_tile_rows(p.kbs);

@@ -50,7 +50,7 @@ def last_status():
 
 
 def make_args(q, k, v, out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
-              softmax_scale, num_q_block, num_k_block, workspace, impl):
+              softmax_scale, num_q_block, num_k_block, workspace, impl, lse=None):
     a = _lib.ForwardArgs()
     a.struct_bytes = ctypes.sizeof(_lib.ForwardArgs)
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
@@ -76,6 +76,7 @@ def make_args(q, k, v, out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size
     a.impl = impl
     a.workspace = workspace.data_ptr()
     a.workspace_bytes = workspace.numel()
+    a.lse = lse.data_ptr() if lse is not None else None
     return a
 
 
@@ -247,3 +248,40 @@ def attention_with_schedule(q, k, v, schedule: MaskSchedule, softmax_scale=None)
             raise RuntimeError(f"hbsa_attention failed ({rc}): {_lib.last_error()}")
         _state["last_workspace"] = s.workspace
     return out
+
+
+def HBSAttention_with_lse(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
+                          softmax_scale=None):
+    """``HBSAttention`` that also returns the natural-log sum of exponentials of every row's allowed scaled
+    scores: ``(out, lse)`` with ``lse`` float32 ``[total_q, nhead_q]``, ``-inf`` for rows that see no key.
+    The reference has no such output (its kernels keep ``log(l)`` without the row maximum,
+    ``fwd_triton_auto_tile_size.py:249``, and drop it); it is what a backward pass starts from."""
+    assert block_mask.dtype == torch.bool, "block_mask must be a boolean tensor"
+    assert block_mask.ndim == 3 and block_mask.shape[0] == k.shape[1], \
+        f"block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block); nheads_k = {k.shape[1]}"
+    assert q.shape[1] % k.shape[1] == 0, "nhead_q must be divisible by nhead_k (for GQA)"
+    assert q_block_size % 16 == 0 and k_block_size % 16 == 0 and q_block_size > 0 and k_block_size > 0, \
+        "q_block_size and k_block_size must be integer multiples of 16."
+    cu_q32, cu_k32 = _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask)
+    lib = _lib.load()
+    dev = q.device
+    nhk, nqb, nkb = block_mask.shape
+    with torch.cuda.device(dev):
+        out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        lse = torch.empty((q.shape[0], q.shape[1]), dtype=torch.float32, device=dev)
+        if q.shape[0] == 0:
+            return out, lse
+        ws = alloc_workspace(nhk, nqb, nkb, cu_q32.numel() - 1, dev)
+        args = make_args(q, k, v, out, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, softmax_scale,
+                         nqb, nkb, ws, _IMPLS[_state["impl"]], lse=lse)
+        rc = lib.hbsa_forward(ctypes.byref(args), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_forward failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+        if _validate_default():
+            status = read_status(ws)
+            assert status[0] != _lib.HBSA_STATUS_BLOCK_COUNT_MISMATCH, \
+                f"block_mask must be a boolean tensor of shape (nheads_k, num_q_block, num_k_block) = ({k.shape[1]}, {status[1]}, {status[2]})"
+            if status[0] != _lib.HBSA_STATUS_OK:
+                raise RuntimeError(f"hbsa_forward: device status {status[0]} (work item {status[3]})")
+    return out, lse

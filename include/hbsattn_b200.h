@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define HBSA_ABI_VERSION 1
+#define HBSA_ABI_VERSION 2
 
 /* Element type of q, k, v and o. */
 enum { HBSA_DTYPE_BF16 = 0, HBSA_DTYPE_F16 = 1, HBSA_DTYPE_F32 = 2 };
@@ -125,6 +125,11 @@ typedef struct hbsa_forward_args {
   int32_t reserved;
   void* workspace;                /* >= hbsa_workspace_bytes(...) bytes, 256-byte aligned    */
   size_t workspace_bytes;
+  float* lse;                     /* NULL, or float32 [total_q, nhead_q] (contiguous): natural-log sum
+                                     of exponentials of every row's allowed scaled scores, -inf for
+                                     rows that see no key.  The reference stores log(l) without the
+                                     row maximum (fwd_triton_auto_tile_size.py:249) and never returns
+                                     it; this is the value a backward pass needs.                */
 } hbsa_forward_args;
 
 int hbsa_forward(const hbsa_forward_args* args, void* stream);

@@ -98,7 +98,7 @@ def oracle_block_decisions(cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size,
 
 
 def oracle_forward(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size,
-                   causal, softmax_scale=None):
+                   causal, softmax_scale=None, return_lse=False):
     """fp32 block-sparse attention forward with the reference's semantics.
 
     For every q-block (``reference.py:46``) the scores against the keys of the
@@ -109,6 +109,12 @@ def oracle_forward(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size
     key set to zero (``:98``), and the result is the fp32 product with V cast
     to ``q.dtype`` (``:100-101``).  GQA: q-head ``h`` uses kv-head
     ``h // (Hq // Hk)`` (``:52``, ``:82``).
+
+    ``return_lse=True`` also returns the natural-log sum of exponentials of every row's
+    allowed scaled scores, fp32 ``[total_q, nhead_q]``, ``-inf`` for rows that see no key.
+    The reference keeps no correct LSE (its Triton kernels store ``log(l)`` without the
+    row maximum, ``fwd_triton_auto_tile_size.py:249``); this is the quantity a backward
+    pass needs.
     """
     cu_q = _as_int_list(cu_q_seqlens)
     cu_k = _as_int_list(cu_k_seqlens)
@@ -122,6 +128,7 @@ def oracle_forward(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size
     assert tuple(block_mask.shape) == (nhead_k, nqb, nkb)
     dev = q.device
     out = torch.empty_like(q)
+    lse = torch.full((q.shape[0], nhead_q), float("-inf"), dtype=torch.float32, device=dev)
     ckb_t = torch.as_tensor(ckb.astype(np.int64), device=dev)
     head_k_of_q = torch.arange(nhead_q, device=dev) // g
     for qb in range(nqb):
@@ -152,7 +159,9 @@ def oracle_forward(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size
         p = torch.softmax(s, dim=1)
         p = torch.nan_to_num(p, nan=0.0)
         out[q0:q1] = torch.einsum("msh,shd->mhd", p, vf)
-    return out
+        if return_lse:
+            lse[q0:q1] = torch.logsumexp(s, dim=1)               # [m, Hq]; -inf where nothing is allowed
+    return (out, lse) if return_lse else out
 
 
 def oracle_active_flops(cu_q_seqlens, cu_k_seqlens, decisions, q_block_size, k_block_size, nhead_q, headdim):

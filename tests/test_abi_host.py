@@ -32,13 +32,13 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.hbsa_version() == 1
+    assert lib.hbsa_version() == 2
 
 
 def test_struct_mirror_size(lib):
     from hbsattn_b200 import _lib
     # 5 size_t/pointers + 12 int64 strides + 3 pointers + 3 int64 + 16 int32/float + 2 pointers/size_t
-    assert ctypes.sizeof(_lib.ForwardArgs) == 8 * 5 + 8 * 12 + 8 * 3 + 8 * 3 + 4 * 16 + 8 * 2
+    assert ctypes.sizeof(_lib.ForwardArgs) == 8 * 5 + 8 * 12 + 8 * 3 + 8 * 3 + 4 * 16 + 8 * 2 + 8
 
 
 def test_workspace_bytes(lib):
