@@ -23,8 +23,13 @@
 //    for P V(t) to complete.
 //  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
 //    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
-//    and no shared-memory exchange.  The running output is rescaled in TMEM only when a row maximum
-//    grows by more than 2^8.
+//    and no shared-memory exchange.  The exponentials of a tile run against the reference maximum of the
+//    previous tiles while the tile's own maximum is computed alongside; the running output is rescaled in
+//    TMEM (and the tile redone) only when a row maximum grows by more than 2^8.  The arithmetic around the
+//    exponentials is two-wide (fma/add/mul.rn.f32x2): the kernel is bound by the instruction stream of these
+//    threads, not by a pipe.
+//  * The last CTA to leave rewinds the work cursor, so one schedule serves any number of launches.  With
+//    `lse` set, ln sum exp of every row goes out beside O.
 //
 // Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp id), warp 4 work
 // fetch + TMA producer, warp 5 TMEM allocator + MMA issuer.  TMEM (256 columns): S0 [0,64), S1 [64,128),
