@@ -538,6 +538,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          uint32_t pmax0 = 0u, pmax1 = 0u;
           bool exact = t == 0;                           // first tile of the item: the maximum must come first
           if (!exact) {
             // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
@@ -555,35 +556,49 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
                 }
                 uint32_t pk[8];
-                max16(&r[16 * j], mx4);
                 exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
                 tmem_st8(tSmine + 8 * j, pk);
+                // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
+                pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
+                pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
+                pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
+                pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
               }
             }
             if (my_nc <= 16) tmem_wait_ld();
-            const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
-            const bool need = mx_s > m_ref + kRescaleThreshold;
+            // A P above 2^8 means the tile exceeds the reference by more than the threshold; the row maximum
+            // itself is only computed on that (rare) path.  Rows without a reference yet take it as well.
+            const uint32_t pm = __vimax3_u16x2(pmax0, pmax1, 0u);
+            const uint32_t p_hi = max(pm >> 16, pm & 0xffffu);
+            bool need = p_hi > (BF16 ? 0x4380u : 0x5c00u) || m_ref == -INFINITY;
             if (TRACE && tid == 0) stamp(P.trace, T, 7);
             if (__any_sync(0xffffffffu, need)) {
-              // O and l move to the new reference maximum; needs the P V product of the previous tile
-              ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
-              if (!ok) break;
-              tc_fence_after();
-              const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
-#pragma unroll 1
-              for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t o[32];
-                tmem_ld32(tOmine + c0, o);
-                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                tmem_st32(tOmine + c0, o);
+              for (int j = 0; j < 4; ++j)
+                if (my_nc > 16 * j) max16(&r[16 * j], mx4);
+              const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
+              need = mx_s > m_ref + kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {       // (a row without reference whose tile is all masked needs nothing)
+                // O and l move to the new reference maximum; needs the P V product of the previous tile
+                ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+                if (!ok) break;
+                tc_fence_after();
+                const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                  uint32_t o[32];
+                  tmem_ld32(tOmine + c0, o);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                  tmem_st32(tOmine + c0, o);
+                }
+                tmem_wait_st();
+                l *= alpha;
+                if (need) m_ref = mx_s;
+                exact = true;                            // P of this tile is recomputed against the new reference
+                sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
               }
-              tmem_wait_st();
-              l *= alpha;
-              if (need) m_ref = mx_s;
-              exact = true;                              // P of this tile is recomputed against the new reference
-              sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
             }
           } else {
             tmem_wait_ld();
