@@ -53,7 +53,7 @@ WORKLOADS = {
 # DRAM bytes per launch of the attention kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
 # capture, profiles/fwd_sm100_kernel_cfg2.md): measured on the batch-2 cut of cfg2 (534.5 MB) and scaled by
 # the number of work items (x4 for batch 8; per-item statistics are identical).
-TRAFFIC_BYTES = {"cfg2_b2": 536.2e6, "cfg2": 4 * 536.2e6}
+TRAFFIC_BYTES = {"cfg2_b2": 536.0e6, "cfg2": 4 * 536.0e6}
 
 # ----------------------------------------------------------------------------------------------
 # synthetic inputs
