@@ -10,7 +10,8 @@ import os
 import threading
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libhbsattn_b200.so")
+# HBSATTN_B200_LIBRARY selects another build of the same library (e.g. the strict-ordering build of build.py --strict).
+LIB_PATH = os.environ.get("HBSATTN_B200_LIBRARY") or os.path.join(PKG_DIR, "libhbsattn_b200.so")
 
 HBSA_DTYPE_BF16, HBSA_DTYPE_F16, HBSA_DTYPE_F32 = 0, 1, 2
 HBSA_IMPL_AUTO, HBSA_IMPL_GENERIC, HBSA_IMPL_SM100 = 0, 1, 2
@@ -29,8 +30,8 @@ EXPORTED_SYMBOLS = (
     "hbsa_select_impl",
     "hbsa_read_status",
     "hbsa_forward_static_scratch",
-    "hbsa_debug_trace_bytes",
-    "hbsa_debug_set_trace",
+    "hbsa_static_scratch_status",
+    "hbsa_debug_set_wait_budget",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -71,6 +72,8 @@ class ForwardArgs(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("lse", ctypes.c_void_p),
+        ("csr_row_ptr", ctypes.c_void_p),
+        ("csr_col_idx", ctypes.c_void_p),
     ]
 
 
@@ -112,11 +115,11 @@ def load() -> ctypes.CDLL:
         lib.hbsa_read_status.argtypes = [vp, vp, vp]
         lib.hbsa_forward_static_scratch.restype = i32
         lib.hbsa_forward_static_scratch.argtypes = [ctypes.POINTER(ForwardArgs), vp]
-        lib.hbsa_debug_trace_bytes.restype = ctypes.c_size_t
-        lib.hbsa_debug_trace_bytes.argtypes = []
-        lib.hbsa_debug_set_trace.restype = None
-        lib.hbsa_debug_set_trace.argtypes = [vp]
-        if lib.hbsa_version() != 2:
+        lib.hbsa_static_scratch_status.restype = i32
+        lib.hbsa_static_scratch_status.argtypes = [vp, vp]
+        lib.hbsa_debug_set_wait_budget.restype = None
+        lib.hbsa_debug_set_wait_budget.argtypes = [ctypes.c_longlong, i32]
+        if lib.hbsa_version() != 3:
             raise ImportError("libhbsattn_b200.so was built from a different ABI version")
         _lib = lib
         return lib

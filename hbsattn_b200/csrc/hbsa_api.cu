@@ -24,8 +24,11 @@ int fail_cuda(cudaError_t e, const char* where) {
 int make_problem(const hbsa_forward_args* a, bool need_tensors, hbsa::Problem* p) {
   if (!a) return fail(HBSA_ERR_NULL, "args is NULL");
   if (a->struct_bytes != sizeof(hbsa_forward_args)) return fail(HBSA_ERR_STRUCT, "hbsa_forward_args.struct_bytes does not match this library");
-  if (!a->cu_q_seqlens || !a->cu_k_seqlens || !a->block_mask || !a->workspace)
-    return fail(HBSA_ERR_NULL, "cu_q_seqlens, cu_k_seqlens, block_mask and workspace must not be NULL");
+  if (!a->cu_q_seqlens || !a->cu_k_seqlens || !a->workspace)
+    return fail(HBSA_ERR_NULL, "cu_q_seqlens, cu_k_seqlens and workspace must not be NULL");
+  if ((a->csr_row_ptr == nullptr) != (a->csr_col_idx == nullptr))
+    return fail(HBSA_ERR_NULL, "csr_row_ptr and csr_col_idx must be given together");
+  if (!a->block_mask && !a->csr_row_ptr) return fail(HBSA_ERR_NULL, "either block_mask or the CSR block mask must be given");
   if (need_tensors && (!a->q || !a->k || !a->v || !a->o)) return fail(HBSA_ERR_NULL, "q, k, v and o must not be NULL");
   if (a->batch <= 0 || a->nhead_q <= 0 || a->nhead_k <= 0 || a->headdim <= 0 || a->num_q_block <= 0 ||
       a->num_k_block <= 0 || a->total_q < 0 || a->total_k < 0)
@@ -43,7 +46,9 @@ int make_problem(const hbsa_forward_args* a, bool need_tensors, hbsa::Problem* p
   if (((uintptr_t)a->workspace) % 256 != 0) return fail(HBSA_ERR_WORKSPACE, "workspace must be 256-byte aligned");
   p->cu_q = a->cu_q_seqlens;
   p->cu_k = a->cu_k_seqlens;
-  p->mask = a->block_mask;
+  p->mask = a->csr_row_ptr ? nullptr : a->block_mask;       // a CSR mask takes precedence
+  p->csr_ptr = a->csr_row_ptr;
+  p->csr_idx = a->csr_col_idx;
   p->mask_s0 = a->mask_stride[0];
   p->mask_s1 = a->mask_stride[1];
   p->mask_s2 = a->mask_stride[2];
@@ -171,9 +176,7 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   return 0;
 }
 
-size_t hbsa_debug_trace_bytes(void) { return hbsa::sm100_trace_bytes(); }
-
-void hbsa_debug_set_trace(void* device_buffer) { hbsa::sm100_set_trace(static_cast<long long*>(device_buffer)); }
+void hbsa_debug_set_wait_budget(long long clocks, int stall_producer) { hbsa::sm100_set_wait_budget(clocks, stall_producer); }
 
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream_) {
   if (!workspace || !status_out) return fail(HBSA_ERR_NULL, "workspace and status_out must not be NULL");

@@ -6,13 +6,14 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <math.h>
 
 #include "../../include/hbsattn_b200.h"
 
 namespace hbsa {
 
 constexpr int kStatusWords = 16;
-constexpr int kItemWords = 12;       // int32 words of one ItemRecord
+constexpr int kItemWords = 16;       // int32 words of one ItemRecord
 
 // Carved out of the caller's workspace by make_workspace(); every pointer is a device pointer.
 struct Workspace {
@@ -27,7 +28,7 @@ struct Workspace {
 };
 
 // Everything the attention kernel needs to know about one (kv-head, q-block) row, written once by
-// the schedule kernel so that a CTA fetches its next piece of work with a single 48-byte load.
+// the schedule kernel so that a CTA fetches its next piece of work with a single 64-byte load.
 // Launch order: kv-head major, then samples from the longest k_len to the shortest, and inside a
 // sample the q-blocks from last to first (under a causal mask the longest rows come first), so the
 // queue drains on short rows and the CTAs that run at the same time share the K/V of a few
@@ -36,6 +37,8 @@ struct __align__(16) ItemRecord {
   int hk, qb, q_begin, q_end;        // kv-head, q-block, token range of the q-block (global)
   int q_in0, k_begin, k_len, kb0;    // in-sample index of the first row; the sample's keys and first k-block
   int n_reach, off, n_tiles, count;  // causal-reachable k-blocks, k_len - q_len, K/V tiles to process, active blocks
+  int csr_begin;                     // CSR block masks: position in col_idx of the row's first active, reachable entry
+  int pad[3];
 };
 static_assert(sizeof(ItemRecord) == kItemWords * 4, "ItemRecord layout");
 
@@ -46,8 +49,10 @@ Workspace make_workspace(void* base, int nhead_k, int num_q_block, int num_k_blo
 struct Problem {
   const int32_t* cu_q;
   const int32_t* cu_k;
-  const uint8_t* mask;
+  const uint8_t* mask;                 // dense block mask, or NULL when the mask is given in CSR form
   int64_t mask_s0, mask_s1, mask_s2;   // bytes
+  const int32_t* csr_ptr;              // CSR block mask: [nhead_k * num_q_block + 1] row starts, or NULL
+  const int32_t* csr_idx;              // [nnz] global k-block indices, ascending inside every row
   int batch, nhead_q, nhead_k, group;  // group = nhead_q / nhead_k
   int headdim;
   int num_q_block, num_k_block, qbs, kbs;
@@ -94,6 +99,31 @@ __device__ __forceinline__ RowGeom row_geometry(const Problem& p, const int32_t*
   return g;
 }
 
+// What the attention kernels do when the schedule kernels left an error status: nothing is computed, and the
+// output is filled with zeros (lse with -inf) so that a caller who does not read the status never sees
+// uninitialised memory.  Called by every thread of every CTA of a one- or two-dimensional grid.
+template <typename T>
+__device__ __forceinline__ void zero_fill_output(T* o, long long s0, long long s1, long long s2, int total_q, int nhead_q,
+                                                 int headdim, float* lse) {
+  const long long n_cta = (long long)gridDim.x * gridDim.y;
+  const long long cta = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+  const long long rows = (long long)total_q * nhead_q;
+  for (long long row = cta; row < rows; row += n_cta) {
+    const long long tok = row / nhead_q, h = row % nhead_q;
+    for (int d = threadIdx.x; d < headdim; d += blockDim.x) o[tok * s0 + h * s1 + d * s2] = T(0.f);
+    if (lse != nullptr && threadIdx.x == 0) lse[row] = -INFINITY;
+  }
+}
+
+// First position in [lo, hi) of the ascending array `a` whose value is >= key (hi if there is none).
+__device__ __forceinline__ int lower_bound_i32(const int32_t* __restrict__ a, int lo, int hi, int key) {
+  while (lo < hi) {
+    const int mid = lo + ((hi - lo) >> 1);
+    if (a[mid] < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
 // printf-style setter of the text hbsa_last_error() returns on the calling thread.
 void set_last_error(const char* fmt, ...);
 
@@ -104,9 +134,9 @@ cudaError_t launch_calculate_blocks(const int32_t* cu_seqlen, int batch, int blo
 cudaError_t launch_schedule(const Problem& p, const Workspace& ws, uint8_t* decisions, cudaStream_t stream);
 // Rows of one K/V tile the tensor-core kernel uses for k blocks of `kbs` rows.
 int sm100_kv_tile_rows(int kbs);
-// Debugging aid: clock64 stamps of the first CTA's pipeline events go to this device buffer.
-void sm100_set_trace(long long* device_buffer);
-size_t sm100_trace_bytes();
+// Debugging aid: clock budget of every wait inside the tensor-core kernel (<= 0: the default), and a mode in
+// which its producer warp publishes nothing, so that every other wait of the kernel runs out.
+void sm100_set_wait_budget(long long clocks, int stall_producer);
 cudaError_t launch_forward_generic(const Problem& p, const Workspace& ws, const hbsa_forward_args& a,
                                    cudaStream_t stream);
 // Returns nullptr when eligible, else a static string saying why not.

@@ -28,9 +28,13 @@ constexpr int kRowsPerCta = 32;
 template <typename T, int DQ, int KT>
 __global__ void __launch_bounds__(128)
 fwd_generic_kernel(Problem p, Workspace ws, const T* __restrict__ q, const T* __restrict__ k,
-                   const T* __restrict__ v, T* __restrict__ o, float* __restrict__ lse, Strides st, int chunks_per_block) {
+                   const T* __restrict__ v, T* __restrict__ o, float* __restrict__ lse, Strides st, int chunks_per_block,
+                   int total_q) {
   constexpr int DPAD = DQ * 4;
-  if (ws.status[0] != HBSA_STATUS_OK) return;
+  if (ws.status[0] != HBSA_STATUS_OK) {
+    zero_fill_output(o, st.o0, st.o1, st.o2, total_q, p.nhead_q, p.headdim, lse);
+    return;
+  }
   extern __shared__ float smem[];
   float* sK = smem;                  // [KT][DPAD]
   float* sV = smem + KT * DPAD;      // [KT][DPAD]
@@ -61,9 +65,21 @@ fwd_generic_kernel(Problem p, Workspace ws, const T* __restrict__ q, const T* __
   int limit_row = g.k_len - 1;
   if (p.causal) limit_row = min(limit_row, qi + g.off);
 
-  const uint8_t* mrow = p.mask + hk * p.mask_s0 + qb * p.mask_s1;
-  for (int j = 0; j < g.n_reach; ++j) {
-    if (mrow[(long long)(g.kb0 + j) * p.mask_s2] == 0) continue;       // uniform over the CTA
+  // Active k-blocks of the row, in ascending order: bytes of the dense mask row, or the entries of the CSR row that
+  // lie in the row's own sample below the causal reach.
+  const bool csr = p.csr_ptr != nullptr;
+  const uint8_t* mrow = csr ? nullptr : p.mask + hk * p.mask_s0 + qb * p.mask_s1;
+  int e_begin = 0, n_src = g.n_reach;
+  if (csr) {
+    const long long row = (long long)hk * p.num_q_block + qb;
+    const int e0 = p.csr_ptr[row], e1 = p.csr_ptr[row + 1];
+    e_begin = lower_bound_i32(p.csr_idx, e0, e1, g.kb0);
+    n_src = lower_bound_i32(p.csr_idx, e_begin, e1, g.kb0 + g.n_reach) - e_begin;
+  }
+  for (int e = 0; e < n_src; ++e) {
+    int j = e;
+    if (csr) j = p.csr_idx[e_begin + e] - g.kb0;
+    else if (mrow[(long long)(g.kb0 + j) * p.mask_s2] == 0) continue;  // uniform over the CTA
     const int blk_k0 = j * p.kbs;
     const int blk_len = min(p.kbs, g.k_len - blk_k0);
     for (int t0 = 0; t0 < blk_len; t0 += KT) {
@@ -139,7 +155,7 @@ static cudaError_t launch_typed(const Problem& p, const Workspace& ws, const hbs
   const T* v = static_cast<const T*>(a.v);
   T* o = static_cast<T*>(a.o);
 #define HBSA_LAUNCH_GENERIC(DQ_, KT_)                                                                   \
-  fwd_generic_kernel<T, DQ_, KT_><<<grid, 128, 2 * KT_ * DQ_ * 4 * sizeof(float), stream>>>(p, ws, q, k, v, o, a.lse, st, cpb)
+  fwd_generic_kernel<T, DQ_, KT_><<<grid, 128, 2 * KT_ * DQ_ * 4 * sizeof(float), stream>>>(p, ws, q, k, v, o, a.lse, st, cpb, a.total_q)
   if (p.headdim <= 32) HBSA_LAUNCH_GENERIC(8, 32);
   else if (p.headdim <= 64) HBSA_LAUNCH_GENERIC(16, 32);
   else if (p.headdim <= 128) HBSA_LAUNCH_GENERIC(32, 32);

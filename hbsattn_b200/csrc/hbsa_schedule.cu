@@ -175,7 +175,8 @@ __global__ void sched_qb2b_kernel(Problem p, Workspace ws) {
 }
 
 // One warp per (kv-head, q-block) row: count the active k-blocks (mask AND same sample AND
-// causal-reachable); optionally write the whole decision row.
+// causal-reachable); optionally write the whole decision row.  The mask is either the dense byte array
+// or a CSR list of k-block indices per row.
 __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace ws, uint8_t* __restrict__ decisions) {
   if (ws.status[0] != HBSA_STATUS_OK) return;
   const int lane = threadIdx.x & 31;
@@ -184,19 +185,31 @@ __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace w
   if (row >= rows) return;
   const int hk = (int)(row / p.num_q_block), qb = (int)(row % p.num_q_block);
   const RowGeom g = row_geometry(p, ws.cnq, ws.cnk, ws.qb2b, qb);
-  const uint8_t* mrow = p.mask + hk * p.mask_s0 + qb * p.mask_s1;
-  int cnt = 0;
-  for (int j = lane; j < g.n_reach; j += 32) cnt += mrow[(long long)(g.kb0 + j) * p.mask_s2] != 0;
+  const int j_last = g.nkb - 1;                 // the ragged last k-block of the sample may own fewer tiles
+  int cnt = 0, csr_begin = 0;
+  bool last_active = false;
+  const uint8_t* mrow = nullptr;
+  if (p.csr_ptr != nullptr) {
+    // CSR row: ascending global k-block indices; the active ones are those of the row's own sample below the causal reach
+    const int e0 = p.csr_ptr[row], e1 = p.csr_ptr[row + 1];
+    csr_begin = lower_bound_i32(p.csr_idx, e0, e1, g.kb0);
+    const int hi = lower_bound_i32(p.csr_idx, csr_begin, e1, g.kb0 + g.n_reach);
+    cnt = hi - csr_begin;
+    last_active = cnt > 0 && j_last < g.n_reach && p.csr_idx[hi - 1] == g.kb0 + j_last;
+  } else {
+    mrow = p.mask + hk * p.mask_s0 + qb * p.mask_s1;
+    for (int j = lane; j < g.n_reach; j += 32) cnt += mrow[(long long)(g.kb0 + j) * p.mask_s2] != 0;
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+    for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+    last_active = cnt > 0 && j_last < g.n_reach && mrow[(long long)(g.kb0 + j_last) * p.mask_s2] != 0;
+  }
   if (lane == 0) {
     ws.counts[row] = cnt;
     int n_tiles = cnt;
     if (p.kv_tile > 0 && p.kv_tile < p.kbs) {
       const int n_sub = p.kbs / p.kv_tile;
       n_tiles = cnt * n_sub;
-      const int j_last = g.nkb - 1;           // the ragged last k-block of the sample may own fewer tiles
-      if (cnt > 0 && j_last < g.n_reach && mrow[(long long)(g.kb0 + j_last) * p.mask_s2] != 0) {
+      if (last_active) {
         const int len_last = g.k_len - j_last * p.kbs;
         n_tiles -= n_sub - (len_last + p.kv_tile - 1) / p.kv_tile;
       }
@@ -205,6 +218,7 @@ __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace w
     rec.hk = hk; rec.qb = qb; rec.q_begin = g.q_begin; rec.q_end = g.q_end;
     rec.q_in0 = g.q_in0; rec.k_begin = g.k_begin; rec.k_len = g.k_len; rec.kb0 = g.kb0;
     rec.n_reach = g.n_reach; rec.off = g.off; rec.n_tiles = n_tiles; rec.count = cnt;
+    rec.csr_begin = csr_begin; rec.pad[0] = rec.pad[1] = rec.pad[2] = 0;
     // launch position: kv-head, then the sample's slot, q-blocks mirrored (last q-block of the sample first)
     const int last = ws.cnq[g.b + 1] - 1;
     const long long pos = (long long)hk * p.num_q_block + (ws.qpos[g.b] + (last - qb));
@@ -212,10 +226,16 @@ __global__ void __launch_bounds__(256) sched_count_kernel(Problem p, Workspace w
   }
   if (decisions) {
     uint8_t* drow = decisions + (size_t)row * p.num_k_block;
-    for (int kb = lane; kb < p.num_k_block; kb += 32) {
-      const int j = kb - g.kb0;
-      const bool act = j >= 0 && j < g.n_reach && mrow[(long long)kb * p.mask_s2] != 0;
-      drow[kb] = act ? 1 : 0;
+    if (p.csr_ptr != nullptr) {
+      for (int kb = lane; kb < p.num_k_block; kb += 32) drow[kb] = 0;
+      __syncwarp();
+      for (int e = csr_begin + lane; e < csr_begin + cnt; e += 32) drow[p.csr_idx[e]] = 1;
+    } else {
+      for (int kb = lane; kb < p.num_k_block; kb += 32) {
+        const int j = kb - g.kb0;
+        const bool act = j >= 0 && j < g.n_reach && mrow[(long long)kb * p.mask_s2] != 0;
+        drow[kb] = act ? 1 : 0;
+      }
     }
   }
 }

@@ -43,6 +43,11 @@ def read_status(workspace: torch.Tensor):
     return list(out)
 
 
+def last_workspace():
+    """Workspace tensor of the most recent forward of this process (its first 16 int32 words are the device status)."""
+    return _state["last_workspace"]
+
+
 def last_status():
     """Status words of the most recent forward on this process (synchronises)."""
     ws = _state["last_workspace"]
@@ -50,7 +55,8 @@ def last_status():
 
 
 def make_args(q, k, v, out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
-              softmax_scale, num_q_block, num_k_block, workspace, impl, lse=None):
+              softmax_scale, num_q_block, num_k_block, workspace, impl, lse=None, csr=None):
+    """``block_mask``: the dense bool mask, or None when ``csr = (row_ptr, col_idx)`` (int32 device tensors) is given."""
     a = _lib.ForwardArgs()
     a.struct_bytes = ctypes.sizeof(_lib.ForwardArgs)
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
@@ -61,9 +67,12 @@ def make_args(q, k, v, out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size
             arr[i] = t.stride(i)
     a.cu_q_seqlens = cu_q_seqlens.data_ptr()
     a.cu_k_seqlens = cu_k_seqlens.data_ptr()
-    a.block_mask = block_mask.data_ptr()
-    for i in range(3):
-        a.mask_stride[i] = block_mask.stride(i)          # bool: one byte per element
+    if block_mask is not None:
+        a.block_mask = block_mask.data_ptr()
+        for i in range(3):
+            a.mask_stride[i] = block_mask.stride(i)      # bool: one byte per element
+    if csr is not None:
+        a.csr_row_ptr, a.csr_col_idx = csr[0].data_ptr(), csr[1].data_ptr()
     a.total_q, a.total_k = q.shape[0], k.shape[0]
     a.nhead_q, a.nhead_k, a.headdim = q.shape[1], k.shape[1], q.shape[2]
     a.batch = cu_q_seqlens.numel() - 1
@@ -110,7 +119,9 @@ class _HBSAttentionFunction(torch.autograd.Function):
         ``block_mask``: bool (nhead_k, num_q_block, num_k_block) over global block indices.
         The eight trailing arguments are the outputs of ``calculate_blocks`` for q and k; they are
         accepted for compatibility (``test/test_accuracy.py:72``) - only the two block counts are used,
-        the tables themselves are rebuilt on the device from ``cu_*_seqlens``.
+        the tables themselves are rebuilt on the device from ``cu_*_seqlens``.  When they are given the call
+        does not synchronise: should the counts contradict ``cu_*_seqlens`` the device notices, computes
+        nothing and returns zeros, and ``last_status()`` reports ``HBSA_STATUS_BLOCK_COUNT_MISMATCH``.
         Returns a contiguous (total_q, nhead_q, headdim) tensor in ``q``'s dtype.
         """
         have_meta = not (num_q_block is None or cu_q_block is None or q_block_to_batch is None or cu_num_q_block is None
@@ -185,6 +196,69 @@ def block_decisions(q, k, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, 
         counts = torch.empty((nhk, nqb), dtype=torch.int32, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = lib.hbsa_block_decisions(ctypes.byref(args), dec.data_ptr(), counts.data_ptr(), stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_block_decisions failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+    return dec.bool(), counts
+
+
+def _check_csr(row_ptr, col_idx, nhead_k, num_q_block):
+    assert row_ptr.is_cuda and col_idx.is_cuda, "the CSR block mask must live on the device"
+    assert row_ptr.dtype == torch.int32 and col_idx.dtype == torch.int32, "csr_row_ptr and csr_col_idx must be int32"
+    assert row_ptr.ndim == 1 and row_ptr.numel() == nhead_k * num_q_block + 1, \
+        f"csr_row_ptr must have nheads_k * num_q_block + 1 = {nhead_k * num_q_block + 1} entries"
+    return row_ptr.contiguous(), col_idx.contiguous()
+
+
+def HBSAttention_csr(q, k, v, cu_q_seqlens, cu_k_seqlens, csr_row_ptr, csr_col_idx, num_q_block, num_k_block,
+                     q_block_size, k_block_size, causal, softmax_scale=None):
+    """``HBSAttention`` with the block mask in CSR form: row ``hk * num_q_block + qb`` of ``csr_row_ptr`` (int32
+    ``[nhead_k * num_q_block + 1]``) owns the global k-block indices ``csr_col_idx[row_ptr[r]:row_ptr[r + 1]]`` (int32,
+    ascending) that q-block ``qb`` of kv-head ``hk`` attends to.  The reference takes dense masks only; this form
+    holds nothing but the active pairs, which is what lets ``hbsattn_b200.shard.pack_units`` put units of different
+    kv-heads into one call.  ``num_q_block`` / ``num_k_block`` are the block counts ``calculate_blocks`` returns."""
+    assert q.shape[1] % k.shape[1] == 0, "nhead_q must be divisible by nhead_k (for GQA)"
+    assert q_block_size % 16 == 0 and k_block_size % 16 == 0 and q_block_size > 0 and k_block_size > 0, \
+        "q_block_size and k_block_size must be integer multiples of 16."
+    cu_q32, cu_k32 = _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, csr_row_ptr)
+    row_ptr, col_idx = _check_csr(csr_row_ptr, csr_col_idx, k.shape[1], num_q_block)
+    lib = _lib.load()
+    dev = q.device
+    with torch.cuda.device(dev):
+        out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        if q.shape[0] == 0:
+            return out
+        ws = alloc_workspace(k.shape[1], num_q_block, num_k_block, cu_q32.numel() - 1, dev)
+        args = make_args(q, k, v, out, cu_q32, cu_k32, None, q_block_size, k_block_size, causal, softmax_scale,
+                         num_q_block, num_k_block, ws, _IMPLS[_state["impl"]], csr=(row_ptr, col_idx))
+        rc = lib.hbsa_forward(ctypes.byref(args), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_forward failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+        if _validate_default():
+            status = read_status(ws)
+            assert status[0] != _lib.HBSA_STATUS_BLOCK_COUNT_MISMATCH, \
+                f"num_q_block / num_k_block must be ({status[1]}, {status[2]}) for these cu_seqlens and block sizes"
+            if status[0] != _lib.HBSA_STATUS_OK:
+                raise RuntimeError(f"hbsa_forward: device status {status[0]} (work item {status[3]})")
+    return out
+
+
+def block_decisions_csr(q, k, cu_q_seqlens, cu_k_seqlens, csr_row_ptr, csr_col_idx, num_q_block, num_k_block,
+                        q_block_size, k_block_size, causal):
+    """``block_decisions`` for a CSR block mask (see ``HBSAttention_csr``)."""
+    cu_q32, cu_k32 = _prepare(q, k, k, cu_q_seqlens, cu_k_seqlens, csr_row_ptr)
+    nhk = k.shape[1]
+    row_ptr, col_idx = _check_csr(csr_row_ptr, csr_col_idx, nhk, num_q_block)
+    lib = _lib.load()
+    dev = q.device
+    with torch.cuda.device(dev):
+        ws = alloc_workspace(nhk, num_q_block, num_k_block, cu_q32.numel() - 1, dev)
+        args = make_args(q, k, k, None, cu_q32, cu_k32, None, q_block_size, k_block_size, causal, 1.0,
+                         num_q_block, num_k_block, ws, _lib.HBSA_IMPL_AUTO, csr=(row_ptr, col_idx))
+        dec = torch.empty((nhk, num_q_block, num_k_block), dtype=torch.uint8, device=dev)
+        counts = torch.empty((nhk, num_q_block), dtype=torch.int32, device=dev)
+        rc = lib.hbsa_block_decisions(ctypes.byref(args), dec.data_ptr(), counts.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
         if rc != 0:
             raise RuntimeError(f"hbsa_block_decisions failed ({rc}): {_lib.last_error()}")
         _state["last_workspace"] = ws

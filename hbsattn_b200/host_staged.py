@@ -14,7 +14,8 @@ from __future__ import annotations
 
 import torch
 
-from .hbsa_interface import HBSAttention
+from . import _lib
+from .hbsa_interface import HBSAttention, last_workspace, read_status
 from .utils import calculate_blocks
 
 
@@ -77,6 +78,7 @@ class HostStagedAttention:
                 o = HBSAttention(dev["q"], dev["k"], dev["v"], dev["cu_q"], dev["cu_k"], dev["mask"], q_block_size,
                                  k_block_size, causal, softmax_scale, tile_mode, *meta_q, *meta_k)
                 self._dev[slot]["out"] = o                         # keeps the tensor alive until the slot is reused
+                self._dev[slot]["workspace"] = last_workspace()    # holds the device status words of this forward
                 self._ev_run[slot] = torch.cuda.Event()
                 self._ev_run[slot].record(self.s_run)
             with torch.cuda.stream(self.s_out):
@@ -95,7 +97,16 @@ class HostStagedAttention:
         return self._ev_out[ticket % self.slots]
 
     def wait(self) -> None:
+        """Blocks until every submitted forward has landed, then reads the device status words of the last forward
+        of every slot: a forward that gave up (``HBSA_STATUS_WAIT_LIMIT``) or found the block counts inconsistent
+        with ``cu_*_seqlens`` raises here instead of handing back zeros silently."""
         with torch.cuda.device(self.device):
             self.s_out.synchronize()
             self.s_run.synchronize()
             self.s_in.synchronize()
+            for slot in self._dev:
+                ws = slot.get("workspace")
+                if ws is not None:
+                    status = read_status(ws)
+                    if status[0] != _lib.HBSA_STATUS_OK:
+                        raise RuntimeError(f"HostStagedAttention: device status {status[0]} (detail {status[1:4]})")

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define HBSA_ABI_VERSION 2
+#define HBSA_ABI_VERSION 3
 
 /* Element type of q, k, v and o. */
 enum { HBSA_DTYPE_BF16 = 0, HBSA_DTYPE_F16 = 1, HBSA_DTYPE_F32 = 2 };
@@ -48,7 +48,7 @@ enum {
 enum {
   HBSA_STATUS_OK = 0,
   HBSA_STATUS_BLOCK_COUNT_MISMATCH = 1, /* num_q_block/num_k_block differ from what cu_seqlens imply;
-                                           the attention kernel did not run                       */
+                                           no attention is computed and `o` is filled with zeros  */
   HBSA_STATUS_WAIT_LIMIT = 2            /* a bounded wait inside the attention kernel ran out       */
 };
 
@@ -130,6 +130,14 @@ typedef struct hbsa_forward_args {
                                      rows that see no key.  The reference stores log(l) without the
                                      row maximum (fwd_triton_auto_tile_size.py:249) and never returns
                                      it; this is the value a backward pass needs.                */
+  const int32_t* csr_row_ptr;     /* NULL, or the block mask in CSR form (block_mask is then ignored and may be
+                                     NULL): int32 [nhead_k * num_q_block + 1], row (hk, qb) owns the entries
+                                     csr_col_idx[csr_row_ptr[hk * num_q_block + qb] .. csr_row_ptr[.. + 1])   */
+  const int32_t* csr_col_idx;     /* int32 [nnz]: GLOBAL k-block indices of the active pairs, ascending inside
+                                     every row; entries that pair blocks of different samples are ignored.
+                                     The reference has no such input: its callers cache calculate_blocks
+                                     outputs by hand (test/test_speedup.py:100-102,152) and the kernels poll
+                                     every mask byte of the sample (fwd_triton_fix_tile_size.py:117-124). */
 } hbsa_forward_args;
 
 int hbsa_forward(const hbsa_forward_args* args, void* stream);
@@ -139,8 +147,9 @@ int hbsa_forward(const hbsa_forward_args* args, void* stream);
  * decode steps) the way the reference's callers reuse calculate_blocks outputs
  * (test/test_speedup.py:100-102,152).
  *   hbsa_build_schedule: block tables from cu_*_seqlens, active k-block count of every
- *       (kv-head, q-block) row, rows ordered by descending work - all into `workspace`
- *       (q, k, v, o are not read and may be NULL).
+ *       (kv-head, q-block) row, and one work record per row in launch order (kv-head major,
+ *       samples from the longest k_len to the shortest, q-blocks of a sample from last to first)
+ *       - all into `workspace` (q, k, v, o are not read and may be NULL).
  *   hbsa_attention: the attention kernel alone; `workspace` must hold the schedule built from the
  *       same cu_*_seqlens, block_mask, block sizes and causal flag.  A schedule serves any number
  *       of launches (the kernel rewinds its work cursor when it finishes); launches that share a
@@ -168,11 +177,13 @@ int hbsa_select_impl(const hbsa_forward_args* args);
  * calls it. */
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
 
-/* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes()
- * bytes is set, the first CTA of every tensor-core attention launch writes clock64() stamps of its
- * pipeline events into it (96 tiles x 32 int64 slots, then start time and SM of the first 512 CTAs).  NULL switches it off (the default). */
-size_t hbsa_debug_trace_bytes(void);
-void hbsa_debug_set_trace(void* device_buffer);
+/* Debugging aid (process-wide, not thread-safe).  Every wait inside the tensor-core attention kernel
+ * gives up after `clocks` ticks of the SM clock (<= 0 restores the default of about two seconds): the
+ * kernel then sets HBSA_STATUS_WAIT_LIMIT, all of its warps leave, and the call returns normally.
+ * With stall_producer != 0 the kernel's loader warp publishes no work at all, so that every other
+ * wait of the kernel runs out with nothing in flight - the way the give-up path is tested.
+ * Applies to launches made after the call. */
+void hbsa_debug_set_wait_budget(long long clocks, int stall_producer);
 
 /*
  * hbsa_forward for callers that cannot allocate: identical to hbsa_forward except that the
@@ -183,16 +194,26 @@ void hbsa_debug_set_trace(void* device_buffer);
  * cudaMalloc).  The call allocates nothing, on the host side of CUDA or on the device.
  *
  *  - Limit: hbsa_workspace_bytes(nhead_k, num_q_block, num_k_block, batch) must not exceed
- *    HBSA_STATIC_SCRATCH_BYTES (about nhead_k * num_q_block <= 80k rows); larger problems
+ *    HBSA_STATIC_SCRATCH_BYTES (about nhead_k * num_q_block <= 60k rows); larger problems
  *    return HBSA_ERR_WORKSPACE and hbsa_last_error() says how many bytes were needed.
  *  - Cost: every GPU that loads the library carries the array until the process exits.
- *  - The first call on each device looks up the array's device address; make that first call
- *    outside any stream capture.
+ *  - The first call on each device looks up the array's device address.  With CUDA's lazy module
+ *    loading this is also when the driver loads the library's device code and places the array,
+ *    so this one call may allocate inside the driver and can fail on a GPU with no memory left:
+ *    make it at start-up, outside any stream capture.  Later calls on that device allocate nothing.
  *  - All calls on a device share the array.  Each call re-initialises what it needs, so
  *    back-to-back calls on one stream are fine; calls that may overlap on the GPU race.
+ *  - The device status words of the last call live in the array; read them with
+ *    hbsa_static_scratch_status (hbsa_read_status needs a workspace pointer the caller does not have).
  */
 #define HBSA_STATIC_SCRATCH_BYTES (4u << 20)
 int hbsa_forward_static_scratch(const hbsa_forward_args* args, void* stream);
+
+/* Copies the 16 device status words of the built-in scratch array of the current device (word 0 =
+ * HBSA_STATUS_* of the last hbsa_forward_static_scratch call there, words 1.. = detail) to
+ * status_out[0..15].  Synchronises `stream`; allocates nothing.  Like the entry point it serves, it
+ * has no counterpart in the reference. */
+int hbsa_static_scratch_status(int32_t* status_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,8 +8,8 @@ sys.path.insert(0, ROOT)
 import torch
 import torch.distributed as dist
 
-from hbsattn_b200.shard import kv_head_range, shard_by_kv_heads
-from oracle import oracle_forward
+from hbsattn_b200.shard import dense_mask_of_csr, pack_units, plan_units, unit_flops, unpack_output
+from oracle import oracle_block_decisions, oracle_forward
 
 
 def _worker(rank, world, port, out_path):
@@ -17,32 +17,38 @@ def _worker(rank, world, port, out_path):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     g = torch.Generator().manual_seed(0)
-    cu_q, cu_k = [0, 48, 112], [0, 80, 131]
-    hq, hk, d = 6, 3, 16
+    cu_q, cu_k = [0, 48, 112, 144], [0, 80, 131, 150]
+    hq, hk, d, qbs, kbs, causal = 6, 3, 16, 32, 16, True
     q = torch.randn(cu_q[-1], hq, d, generator=g)
     k = torch.randn(cu_k[-1], hk, d, generator=g)
     v = torch.randn(cu_k[-1], hk, d, generator=g)
-    mask = torch.rand(hk, 4, 5, generator=g) < 0.6
-    qs, ks, vs, ms, q_slice = shard_by_kv_heads(q, k, v, mask, rank, world)
-    mine = oracle_forward(qs, ks, vs, cu_q, cu_k, ms, 32, 32, True, None)
-    parts = [torch.empty(cu_q[-1], (kv_head_range(hk, r, world)[1] - kv_head_range(hk, r, world)[0]) * (hq // hk), d)
-             for r in range(world)]
-    dist.all_gather(parts, mine.contiguous()) if len({p.shape for p in parts}) == 1 else None
-    if len({p.shape for p in parts}) != 1:                      # uneven shards: gather through object lists
-        objs = [None] * world
-        dist.all_gather_object(objs, mine)
-        parts = objs
+    mask = torch.rand(hk, 5, 11, generator=g) < 0.6
+    # every rank derives the same plan from the same decisions
+    dec = oracle_block_decisions(cu_q, cu_k, mask, qbs, kbs, causal)
+    flops = unit_flops(dec, cu_q, cu_k, qbs, kbs, d, hq // hk)
+    plan = plan_units(flops, world)
+    mine = pack_units(plan[rank], q, k, v, cu_q, cu_k, mask, qbs, kbs)
+    # the oracle takes a dense mask: expand this rank's CSR rows (the GPU path consumes the CSR form directly)
+    dense = dense_mask_of_csr(mine.csr_row_ptr, mine.csr_col_idx, 1, mine.num_q_block, mine.num_k_block)
+    out = oracle_forward(mine.q, mine.k, mine.v, mine.cu_q_seqlens.tolist(), mine.cu_k_seqlens.tolist(), dense, qbs, kbs, causal, None)
+    parts = [None] * world
+    dist.all_gather_object(parts, (plan[rank], mine.q_rows, out))
     t = torch.tensor([1.0 + rank, 10.0 * (rank + 1)], dtype=torch.float64)
     tmax, wsum = t[:1].clone(), t[1:].clone()
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     dist.all_reduce(wsum, op=dist.ReduceOp.SUM)
     if rank == 0:
-        full = oracle_forward(q, k, v, cu_q, cu_k, mask, 32, 32, True, None)
-        got = torch.cat(parts, dim=1)
-        torch.save({"err": (full - got).abs().max().item(), "tmax": tmax.item(), "wsum": wsum.item()}, out_path)
+        full = oracle_forward(q, k, v, cu_q, cu_k, mask, qbs, kbs, causal, None)
+        got = torch.full_like(full, float("nan"))
+        seen = []
+        for units, rows, o in parts:
+            mine.units, mine.q_rows = units, rows           # reuse the container for unpacking the other rank's part
+            unpack_output(mine, o, got)
+            seen += list(units)
+        torch.save({"err": (full - got).abs().max().item(), "tmax": tmax.item(), "wsum": wsum.item(),
+                    "units": sorted(seen), "all_units": sorted((b, h) for b in range(len(cu_q) - 1) for h in range(hk))}, out_path)
     dist.barrier()
     dist.destroy_process_group()
-
 
 
 if __name__ == "__main__":

@@ -32,13 +32,13 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.hbsa_version() == 2
+    assert lib.hbsa_version() == 3
 
 
 def test_struct_mirror_size(lib):
     from hbsattn_b200 import _lib
     # 5 size_t/pointers + 12 int64 strides + 3 pointers + 3 int64 + 16 int32/float + 2 pointers/size_t
-    assert ctypes.sizeof(_lib.ForwardArgs) == 8 * 5 + 8 * 12 + 8 * 3 + 8 * 3 + 4 * 16 + 8 * 2 + 8
+    assert ctypes.sizeof(_lib.ForwardArgs) == 8 * 5 + 8 * 12 + 8 * 3 + 8 * 3 + 4 * 16 + 8 * 2 + 8 + 8 * 2
 
 
 def test_workspace_bytes(lib):
@@ -46,7 +46,7 @@ def test_workspace_bytes(lib):
     small = lib.hbsa_workspace_bytes(2, 5, 12, 5)
     big = lib.hbsa_workspace_bytes(32, 4096, 4096, 8)
     assert 0 < small < big and small % 256 == 0 and big % 256 == 0
-    assert big < 8 * 1024 * 1024          # a few ints per (kv-head, q-block) row, independent of num_k_block
+    assert big < 12 * 1024 * 1024         # a few ints per (kv-head, q-block) row, independent of num_k_block
 
 
 def _args(**over):
