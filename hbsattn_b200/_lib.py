@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "hbsa_forward_static_scratch",
     "hbsa_static_scratch_status",
     "hbsa_debug_set_wait_budget",
+    "hbsa_debug_trace_bytes",
+    "hbsa_debug_set_trace",
 )
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -117,6 +119,10 @@ def load() -> ctypes.CDLL:
         lib.hbsa_forward_static_scratch.argtypes = [ctypes.POINTER(ForwardArgs), vp]
         lib.hbsa_static_scratch_status.restype = i32
         lib.hbsa_static_scratch_status.argtypes = [vp, vp]
+        lib.hbsa_debug_trace_bytes.restype = ctypes.c_size_t
+        lib.hbsa_debug_trace_bytes.argtypes = []
+        lib.hbsa_debug_set_trace.restype = None
+        lib.hbsa_debug_set_trace.argtypes = [vp]
         lib.hbsa_debug_set_wait_budget.restype = None
         lib.hbsa_debug_set_wait_budget.argtypes = [ctypes.c_longlong, i32]
         if lib.hbsa_version() != 3:

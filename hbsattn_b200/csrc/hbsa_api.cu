@@ -176,6 +176,10 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   return 0;
 }
 
+size_t hbsa_debug_trace_bytes(void) { return hbsa::sm100_trace_bytes(); }
+
+void hbsa_debug_set_trace(void* device_buffer) { hbsa::sm100_set_trace(static_cast<long long*>(device_buffer)); }
+
 void hbsa_debug_set_wait_budget(long long clocks, int stall_producer) { hbsa::sm100_set_wait_budget(clocks, stall_producer); }
 
 int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream_) {

@@ -137,6 +137,9 @@ int sm100_kv_tile_rows(int kbs);
 // Debugging aid: clock budget of every wait inside the tensor-core kernel (<= 0: the default), and a mode in
 // which its producer warp publishes nothing, so that every other wait of the kernel runs out.
 void sm100_set_wait_budget(long long clocks, int stall_producer);
+// Debugging aid: clock64 stamps of the first CTA's pipeline events go to this device buffer (NULL: off).
+void sm100_set_trace(long long* device_buffer);
+size_t sm100_trace_bytes();
 cudaError_t launch_forward_generic(const Problem& p, const Workspace& ws, const hbsa_forward_args& a,
                                    cudaStream_t stream);
 // Returns nullptr when eligible, else a static string saying why not.

@@ -96,6 +96,33 @@ struct Sm100Params {
   int debug_stall;             // debugging aid: the producer publishes nothing, every wait runs out
   float scale_log2;
   long long wait_budget;       // clock64 ticks
+  long long* trace;            // debugging aid: clock64 stamps of CTA 0 (NULL in normal use)
+};
+
+// Debugging aid.  While a trace buffer is set, four threads of CTA 0 (the MMA thread, the first thread of each
+// lane's softmax warps, the first thread of the producer warp) write (clock64 << 8 | code) stamps of their
+// pipeline events into their own region of kTraceCap entries; entry 0 of a region holds the number of stamps.
+// The shipped instantiation carries no stamp code at all.
+constexpr int kTraceCap = 8192;
+constexpr int kTraceRegions = 4;
+template <bool TRACE>
+struct Tracer {
+  long long* base;
+  int n;
+  __device__ __forceinline__ void init(long long* buf, int region, bool mine) {
+    base = (TRACE && buf != nullptr && mine && blockIdx.x == 0) ? buf + (size_t)region * kTraceCap : nullptr;
+    n = 1;
+  }
+  __device__ __forceinline__ void put(int code) {
+    if (TRACE) {
+      if (base != nullptr && n < kTraceCap) base[n++] = (clock64() << 8) | (long long)code;
+    }
+  }
+  __device__ __forceinline__ void done() {
+    if (TRACE) {
+      if (base != nullptr) base[0] = n - 1;
+    }
+  }
 };
 
 // What the producer tells the other warps about one work item.
@@ -121,11 +148,30 @@ struct __align__(16) Control {
   ItemSlot slot[2][2];
 };
 
+// Compile-time tuning knobs of the softmax threads (see exp16):
+//   HBSA_POLY_PAIRS  of every 8 column pairs, how many take their exponentials from a polynomial on the FMA pipe
+//                    instead of the exp unit (0..8); only bf16/fp16 tiles without masked columns use it
+//   HBSA_ALU_PACK    1: fp32 -> bf16 pairs are packed with integer adds and a byte permute instead of cvt
+#ifndef HBSA_POLY_PAIRS
+#define HBSA_POLY_PAIRS 0
+#endif
+#ifndef HBSA_ALU_PACK
+#define HBSA_ALU_PACK 0
+#endif
+
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t r;
   if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+// P >= 0 and finite-or-inf: rounding to bf16 is "add half an ulp of the kept part, keep the upper 16 bits" (ties go
+// up instead of to even, one ulp apart once in 2^16 values).  The conversion instruction shares the exp unit, which is
+// the pipe the softmax threads saturate; these three run on the integer pipe.
+template <bool BF16> __device__ __forceinline__ uint32_t pack2_p(float lo, float hi) {
+  if (BF16 && HBSA_ALU_PACK)
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+  return pack2<BF16>(lo, hi);
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -146,21 +192,55 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[2] = max3(mx[2], __uint_as_float(r[12]), __uint_as_float(r[13]));
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
+// 2^x for two values by polynomial on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f from a
+// cubic (relative error 7.5e-5, far below the 2^-9 of the 16-bit P it is rounded to); n goes straight into the
+// exponent field.  x is clamped to [-126, 255]: below, the result is a tiny normal number; above 128 the exponent
+// overflows into a bit pattern that, read as an unsigned 16-bit float, is larger than any legal P - exactly what
+// the staleness check of the caller looks for.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  ptx::unpack_f32x2(x2, x0, x1);
+  x0 = fminf(fmaxf(x0, -126.f), 255.f);
+  x1 = fminf(fmaxf(x1, -126.f), 255.f);
+  const uint64_t xc = ptx::pack_f32x2(x0, x1);
+  const uint64_t magic = ptx::pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23: the sum's low mantissa bits are round(x)
+  const uint64_t t = ptx::add_f32x2(xc, magic);
+  const uint64_t n = ptx::add_f32x2(t, ptx::pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = ptx::fma_f32x2(n, ptx::pack_f32x2(-1.f, -1.f), xc);
+  uint64_t q = ptx::fma_f32x2(f, ptx::pack_f32x2(0.05517164617776871f, 0.05517164617776871f), ptx::pack_f32x2(0.2426111251115799f, 0.2426111251115799f));
+  q = ptx::fma_f32x2(q, f, ptx::pack_f32x2(0.6932609677314758f, 0.6932609677314758f));
+  q = ptx::fma_f32x2(q, f, ptx::pack_f32x2(0.9999280571937561f, 0.9999280571937561f));
+  float q0, q1, t0, t1;
+  ptx::unpack_f32x2(q, q0, q1);
+  ptx::unpack_f32x2(t, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 // P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
 // The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe time, half the
-// issue slots.
-template <bool BF16>
+// issue slots.  POLY of the 8 column pairs take the polynomial (callers pass 0 for tiles with masked columns:
+// -inf must come out as an exact zero).
+template <bool BF16, int POLY>
 __device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
   const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2), neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
   uint64_t sa = ptx::pack_f32x2(sum[0], sum[2]), sb = ptx::pack_f32x2(sum[1], sum[3]);
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    float x0, x1;
-    ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2), x0, x1);
-    const float p0 = ptx::ex2_approx(x0), p1 = ptx::ex2_approx(x1);
-    if ((i >> 1) & 1) sb = ptx::add_f32x2(sb, ptx::pack_f32x2(p0, p1));
+    const int q = i >> 1;
+    const uint64_t x2 = ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2);
+    float p0, p1;
+    if (((q + 1) * POLY) / 8 > (q * POLY) / 8) {
+      exp2_poly2(x2, p0, p1);
+    } else {
+      float x0, x1;
+      ptx::unpack_f32x2(x2, x0, x1);
+      p0 = ptx::ex2_approx(x0);
+      p1 = ptx::ex2_approx(x1);
+    }
+    if (q & 1) sb = ptx::add_f32x2(sb, ptx::pack_f32x2(p0, p1));
     else sa = ptx::add_f32x2(sa, ptx::pack_f32x2(p0, p1));
-    pk[i >> 1] = pack2<BF16>(p0, p1);
+    pk[q] = pack2_p<BF16>(p0, p1);
   }
   ptx::unpack_f32x2(sa, sum[0], sum[2]);
   ptx::unpack_f32x2(sb, sum[1], sum[3]);
@@ -215,7 +295,7 @@ struct MmaLane {
   int I, Iq, Ipv, T;         // items seen, items whose first S / first P V was issued, tiles
 };
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
@@ -305,6 +385,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       st[L].blk = -1; st[L].sub = 0; st[L].I = 0; st[L].Iq = 0; st[L].T = 0;
     }
     RingPos rp = {0, 0u};
+    Tracer<TRACE> tr;
+    tr.init(P.trace, 3, lane == 0);
     const bool csr = p.csr_ptr != nullptr;
     bool ok = P.debug_stall == 0;
     // Two claims ahead: the record of the candidate item is on its way while the current items run, and the
@@ -318,12 +400,26 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     next_idx = __shfl_sync(0xffffffffu, next_idx, 0);
     ItemRecord cand_rec = {};
     if (cand_idx < P.total_items) cand_rec = records[cand_idx / P.items_per_row];
+    // The first 32 mask entries of the candidate's row are requested one turn after its record, so that neither load
+    // is waited for when a lane takes the candidate.
+    bool cand_bits_req = false, cand_bit = false;
+    int cand_val = 0;
+    auto request_cand_bits = [&]() {
+      if (csr) {
+        cand_val = lane < cand_rec.count ? p.csr_idx[cand_rec.csr_begin + lane] - cand_rec.kb0 : 0;
+      } else {
+        const uint8_t* mrow = p.mask + cand_rec.hk * p.mask_s0 + cand_rec.qb * p.mask_s1 + (long long)cand_rec.kb0 * p.mask_s2;
+        cand_bit = lane < cand_rec.n_reach && mrow[(long long)lane * p.mask_s2] != 0;
+      }
+      cand_bits_req = true;
+    };
 
     auto acquire = [&]() -> bool {                       // the ring slot at rp is free again
       return warp_wait(bar_ring_empty + 8u * (uint32_t)rp.slot, rp.phase ^ 1u, abort_flag, budget);
     };
 
     auto turn = [&](ProdLane& s, const int L) {
+      if (!cand_bits_req && cand_idx < P.total_items) request_cand_bits();
       if (s.pend_v) {
         if (!acquire()) { ok = false; return; }
         if (lane == 0) {
@@ -335,15 +431,20 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         rp.advance(P.n_slots);
         s.pend_v = false;
+        tr.put(0x10 + L);
       }
       if (s.done) return;
       while (s.tiles_left == 0) {
         // ---- next work item of this lane
         const long long idx = cand_idx;
         const bool have = idx < P.total_items;
+        if (have && !cand_bits_req) request_cand_bits();
         const ItemRecord rec = cand_rec;
+        const bool rec_bit = cand_bit;
+        const int rec_val = cand_val;
         const int rem = have ? (int)(idx % P.items_per_row) : 0;
         cand_idx = next_idx;
+        cand_bits_req = false;
         if (have) {
           if (cand_idx < P.total_items) cand_rec = records[cand_idx / P.items_per_row];
           if (lane == 0) next_idx = (long long)atomicAdd(cursor, 1ull);
@@ -369,6 +470,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mbar_arrive(bar2(bar_item_full + 16u * L, s.I));
         }
         ++s.I;
+        tr.put(0x20 + L);
         if (!have) { s.done = true; return; }
         if (n_tiles <= 0) continue;
         // Q of the lane has one buffer: the last S of the lane's previous item must be done
@@ -381,6 +483,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tma_load_3d(sQ + (uint32_t)L * Q_BYTES + pn * (128u * 128u), &tm_q, bar, pn * 64, head0, tile_tok0);
         }
         ++s.Iq;
+        tr.put(0x30 + L);
         s.hk = rec.hk;
         s.tiles_left = n_tiles;
         s.n_reach = rec.n_reach;
@@ -394,11 +497,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (csr) {
           s.cidx = p.csr_idx + rec.csr_begin;
           s.n_src = rec.count;
-          s.val_next = lane < s.n_src ? s.cidx[lane] - s.kb0 : 0;
+          s.val_next = rec_val;
         } else {
           s.mrow = p.mask + rec.hk * p.mask_s0 + rec.qb * p.mask_s1 + (long long)rec.kb0 * p.mask_s2;
           s.n_src = rec.n_reach;
-          s.bit_next = lane < s.n_src && s.mrow[(long long)lane * p.mask_s2] != 0;
+          s.bit_next = rec_bit;
         }
       }
       // ---- first row (in-sample) of the lane's next active K/V tile
@@ -439,6 +542,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(dst + pn * kv_panel_bytes, &tm_k, bar, pn * 64, s.hk, s.k_begin + k0);
       }
       rp.advance(P.n_slots);
+      tr.put(0x40 + L);
       s.pend_v = true;
       s.pend_tok = s.k_begin + k0;
       ++s.T;
@@ -450,6 +554,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!ok) break;
       turn(st[1], 1);
     }
+    tr.done();
     // Copies that were issued are always waited for by the MMA thread (it gives up only on barriers
     // of its own sequence), and the CTA does not retire before that thread is through.
   } else if (warp == kMmaWarp) {
@@ -486,6 +591,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ml[L].I = 0; ml[L].Iq = 0; ml[L].Ipv = 0; ml[L].T = 0;
       }
       RingPos rc = {0, 0u};
+      Tracer<TRACE> tr;
+      tr.init(P.trace, 0, true);
       bool ok = true;
       auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
         const bool r = mbar_wait_bounded(bar, parity, abort_flag, budget);
@@ -500,25 +607,31 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint32_t tO = tmem_base + kTmemOBase + (uint32_t)L * D;
         if (s.pend) {
           // ---- O (+)= P V of the lane's tile in flight; its V tile is the next ring entry
+          tr.put(0x10 + L);
           if (!wait(bar_ring_full + 8u * (uint32_t)rc.slot, rc.phase)) { ok = false; return; }
+          tr.put(0x20 + L);
           // the first P V of an item overwrites O: the epilogue of the lane's previous item must have read it
           if (s.pend_first && s.Ipv >= 1 && !wait(bar_o_free + 8u * L, (uint32_t)(s.Ipv - 1) & 1u)) { ok = false; return; }
           const uint32_t v_lo = v_lo0 + (uint32_t)rc.slot * slot_units;
           const uint32_t par = (uint32_t)s.pend_T & 1u;
           if (!wait(bar_p_full + 16u * L, par)) { ok = false; return; }
+          tr.put(0x30 + L);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             if (ks < ks0) mma_ts(tO, tS + (uint32_t)ks * 8u, smem_desc_join(v_lo + (uint32_t)ks * 128u, desc_hi), idesc_pv,
                                  (s.pend_first && ks == 0) ? 0u : 1u);
           tc_commit(pv_bar(bar_pv_done, L, 0, s.pend_T));
+          tr.put(0x40 + L);
           if (ks1 > 0) {
             if (!wait(bar_p_full + 16u * L + 8u, par)) { ok = false; return; }
+            tr.put(0x50 + L);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
               if (ks < ks1) mma_ts(tO, tS + 32u + (uint32_t)ks * 8u, smem_desc_join(v_lo + (uint32_t)(4 + ks) * 128u, desc_hi), idesc_pv, 1u);
             tc_commit(pv_bar(bar_pv_done, L, 1, s.pend_T));
           }
           tc_commit(bar_ring_empty + 8u * (uint32_t)rc.slot);
+          tr.put(0x60 + L);
           rc.advance(P.n_slots);
           if (s.pend_first) ++s.Ipv;
           if (s.pend_last) mbar_arrive(bar2(bar_item_done + 16u * L, s.pend_item));   // through with the item
@@ -538,8 +651,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           s.first = true;
         }
         // ---- S = Q K^T of the lane's next tile; its K tile is the next ring entry
+        tr.put(0x70 + L);
         if (!wait(bar_ring_full + 8u * (uint32_t)rc.slot, rc.phase)) { ok = false; return; }
+        tr.put(0x80 + L);
         if (s.first && !wait(bar_q_full + 8u * L, (uint32_t)s.Iq & 1u)) { ok = false; return; }
+        tr.put(0x90 + L);
 #ifdef HBSA_STRICT_TCGEN05
         // every P V group of the lane has completed before S overwrites the columns of P
         if (s.T >= 1 && !wait(pv_bar(bar_pv_done, L, ks1 > 0 ? 1 : 0, s.T - 1), pv_par(s.T - 1))) { ok = false; return; }
@@ -557,6 +673,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_commit(bar_s_full + 8u * L);
         tc_commit(bar_ring_empty + 8u * (uint32_t)rc.slot);
         if (s.tiles_left == 1) tc_commit(bar_q_free + 8u * L);             // the lane's Q buffer may be refilled
+        tr.put(0xa0 + L);
         rc.advance(P.n_slots);
         s.pend = true;
         s.pend_first = s.first;
@@ -573,6 +690,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!ok) break;
         turn(ml[1], 1);
       }
+      tr.done();
       // Every product issued so far has completed before the CTA gives TMEM back (bounded).
       tc_commit(bar_drain);
       mbar_wait_bounded(bar_drain, 0u, abort_flag, budget);
@@ -587,6 +705,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tOmine = tmem_base + kTmemOBase + (uint32_t)L * D + lane_off;
     const float scale_log2 = P.scale_log2;
     const int n_half = nt1 > 0 ? 2 : 1;
+    Tracer<TRACE> tr;
+    tr.init(P.trace, 1 + L, wq == 0 && lane == 0);
     int I = 0, T = 0;
     bool ok = true;
     while (ok) {
@@ -595,6 +715,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const volatile ItemSlot* sl = &ctl->slot[L][I & 1];
       const int n_tiles = sl->n_tiles;
       if (n_tiles < 0) break;
+      tr.put(0x10);
       const int tile_tok0 = sl->tile_tok0, head0 = sl->head0, q_end = sl->q_end;
       const int r_tok = tile_tok0 + (row >> P.gp_shift), r_head = head0 + (row & (P.gp - 1));
       if (n_tiles == 0) {
@@ -613,24 +734,26 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = warp_wait(bar_s_full + 8u * L, (uint32_t)T & 1u, abort_flag, budget);
           if (!ok) break;
           tc_fence_after();
+          tr.put(0x20);
           const int tile_col0 = ctl->tile_k0[L][T & (kTileInfo - 1)];
           for (int h = 0; h < n_half && ok; ++h) {
             const int my_nc = h == 0 ? nt0 : nt1;                          // columns of this half: 16, 32, 48 or 64
             const int col_limit = limit_row - tile_col0 - h * kSubCols;    // columns <= col_limit are valid
             const uint32_t tSmine = tSlane + (uint32_t)h * kSubCols;       // S of this half
             const uint32_t tPmine = tSlane + (uint32_t)h * (kSubCols / 2); // P of this half (16-bit pairs)
-
-            // ---- this thread's row of S, all in registers (P of the second half lands on S columns of the
-            //      first half, which are in registers by then).  The first 16 columns are awaited alone so
-            //      that work on them overlaps the TMEM latency of the rest.
+            // on the causal diagonal or at the ragged end of the sample; decided per warp, because the two code paths
+            // below both contain warp-wide TMEM stores (rows that are not on the edge mask nothing)
+            const bool edge = __any_sync(0xffffffffu, col_limit < my_nc - 1);
+            // ---- this thread's row of S of this half, all in registers before its first P is stored (P of the second
+            //      half lands on S columns of the first half, which are in registers by then).  Load and wait stay in
+            //      one straight piece of code: the registers of an asynchronous TMEM load must not be moved by the
+            //      compiler before the wait.
             uint32_t r[64];
-            const bool edge = col_limit < my_nc - 1;      // on the causal diagonal or at the ragged end of the sample
-            tmem_ld16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
-            tmem_wait_ld();
 #pragma unroll
-            for (int j = 1; j < 4; ++j)
+            for (int j = 0; j < 4; ++j)
               if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
-
+            tmem_wait_ld();
+            if (h == 0) tr.put(0x21);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pmax0 = 0u, pmax1 = 0u;
@@ -640,26 +763,38 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               // reference gives the same softmax; it only has to keep P in range).  If a P turns out to
               // exceed 2^8, the exact pass below redoes these columns.
               const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
+              if (edge) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (my_nc > 16 * j) {
-                  if (j == 1) tmem_wait_ld();
-                  if (edge) {
+                for (int j = 0; j < 4; ++j) {
+                  if (my_nc > 16 * j) {
 #pragma unroll
                     for (int i = 16 * j; i < 16 * j + 16; ++i)
                       if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
+                    uint32_t pk[8];
+                    exp16<BF16, 0>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                    tmem_st8(tPmine + 8 * j, pk);
+                    pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
+                    pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
+                    pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
+                    pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
                   }
-                  uint32_t pk[8];
-                  exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
-                  tmem_st8(tPmine + 8 * j, pk);
-                  // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
-                  pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
-                  pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
-                  pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
-                  pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (my_nc > 16 * j) {
+                    uint32_t pk[8];
+                    exp16<BF16, HBSA_POLY_PAIRS>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                    tmem_st8(tPmine + 8 * j, pk);
+                    // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
+                    pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
+                    pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
+                    pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
+                    pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
+                  }
                 }
               }
-              if (my_nc <= 16) tmem_wait_ld();
+              tr.put(0x22);
               // A P above 2^8 means the columns exceed the reference by more than the threshold; the row maximum
               // itself is only computed on that (rare) path.  Rows without a reference yet take it as well.
               const uint32_t pm = __vimax3_u16x2(pmax0, pmax1, 0u);
@@ -695,7 +830,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
               }
             } else {
-              tmem_wait_ld();
               if (edge) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
@@ -713,16 +847,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               for (int j = 0; j < 4; ++j) {
                 if (my_nc > 16 * j) {
                   uint32_t pk[8];
-                  exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+                  exp16<BF16, 0>(&r[16 * j], pk, scale_log2, neg_m, sum);
                   tmem_st8(tPmine + 8 * j, pk);
                 }
               }
             }
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            tr.put(0x23);
             tmem_wait_st();
+            tr.put(0x24);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p_full + 16u * L + 8u * (uint32_t)h);   // one arrival per warp
+            tr.put(0x30 + h);
           }
         }
         if (!ok) break;
@@ -736,44 +873,53 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // ln sum exp of the row's scaled scores = ln 2 * (reference + log2 l), whatever reference was used
           P.lse[(long long)r_tok * p.nhead_q + r_head] = live ? 0.6931471805599453f * (m_ref + log2f(l)) : -INFINITY;
         }
+        tr.put(0x40);
         ok = warp_wait(pv_bar(bar_pv_done, L, n_half - 1, T - 1), pv_par(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
+        tr.put(0x50);
         OutT* const orow = o_base + r_tok * P.o_s0 + r_head * P.o_s1;
+        // 64 columns of O per TMEM round trip (128 would not fit the registers of a thread beside the packing)
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t oa[32];
-          tmem_ld32(tOmine + c0, oa);
+        for (int cb = 0; cb < D; cb += 64) {
+          uint32_t oa[64];
+          tmem_ld32(tOmine + cb, *reinterpret_cast<uint32_t(*)[32]>(&oa[0]));
+          tmem_ld32(tOmine + cb + 32, *reinterpret_cast<uint32_t(*)[32]>(&oa[32]));
           tmem_wait_ld();
-          if (c0 + 32 >= D) {
+          if (cb + 64 >= D) {
             tc_fence_before();                                             // O is in registers: the lane's next item may overwrite it
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_o_free + 8u * L);
           }
-          uint32_t w[16];
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float y0, y1;
-            unpack_f32x2(mul_f32x2(pack_b32x2(oa[e], oa[e + 1]), inv2), y0, y1);
-            w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
-          }
-          if (store_row) {
-            // this thread's 64 bytes of the row: two 256-bit stores when the rows are 32-byte aligned
-            if (P.o_vec32) {
-              st_global_v8(orow + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
-              st_global_v8(orow + c0 + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
-            } else {
+          for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t w[16];
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                *reinterpret_cast<uint4*>(orow + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            for (int e = 0; e < 32; e += 2) {
+              float y0, y1;
+              unpack_f32x2(mul_f32x2(pack_b32x2(oa[c0 + e], oa[c0 + e + 1]), inv2), y0, y1);
+              w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
+            }
+            if (store_row) {
+              // this thread's 64 bytes of the row: two 256-bit stores when the rows are 32-byte aligned
+              if (P.o_vec32) {
+                st_global_v8(orow + cb + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+                st_global_v8(orow + cb + c0 + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  *reinterpret_cast<uint4*>(orow + cb + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              }
             }
           }
         }
+        tr.put(0x60);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar2(bar_item_done + 16u * L, I));
       ++I;
     }
+    tr.done();
   }
 
   // ---- teardown: every thread gets here (all waits are bounded)
@@ -841,6 +987,7 @@ int sm_count() {
   return cached[dev];
 }
 
+long long* g_trace = nullptr;
 long long g_wait_budget = 4000000000ll;   // clock64 ticks a wait inside the kernel may take (about two seconds)
 int g_debug_stall = 0;
 
@@ -850,6 +997,9 @@ void sm100_set_wait_budget(long long clocks, int stall_producer) {
   g_wait_budget = clocks > 0 ? clocks : 4000000000ll;
   g_debug_stall = stall_producer ? 1 : 0;
 }
+
+void sm100_set_trace(long long* device_buffer) { g_trace = device_buffer; }
+size_t sm100_trace_bytes() { return (size_t)kTraceRegions * kTraceCap * sizeof(long long); }
 
 int sm100_kv_tile_rows(int kbs) {
   if (kbs <= kTileRowsMax) return kbs;
@@ -902,6 +1052,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.scale_log2 = p.scale * 1.4426950408889634f;
   P.wait_budget = g_wait_budget;
   P.debug_stall = g_debug_stall;
+  P.trace = g_trace;
   P.o_vec32 = ((uintptr_t)a.o % 32 == 0 && (a.o_stride[0] * 2) % 32 == 0 && (a.o_stride[1] * 2) % 32 == 0) ? 1 : 0;
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
@@ -930,16 +1081,18 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   }
 
   cudaError_t e = cudaSuccess;
-#define HBSA_LAUNCH_SM100(D_, BF_)                                                                        \
+#define HBSA_LAUNCH_SM100(D_, BF_, TR_)                                                                   \
   do {                                                                                                   \
-    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, TR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) {                                                                              \
-      fwd_sm100_kernel<D_, BF_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                        \
+      fwd_sm100_kernel<D_, BF_, TR_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                   \
       e = cudaGetLastError();                                                                            \
     }                                                                                                    \
   } while (0)
-  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100(128, true); else HBSA_LAUNCH_SM100(128, false); }
-  else { if (bf16) HBSA_LAUNCH_SM100(64, true); else HBSA_LAUNCH_SM100(64, false); }
+#define HBSA_LAUNCH_SM100_T(D_, BF_) do { if (P.trace != nullptr) HBSA_LAUNCH_SM100(D_, BF_, true); else HBSA_LAUNCH_SM100(D_, BF_, false); } while (0)
+  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
+  else { if (bf16) HBSA_LAUNCH_SM100_T(64, true); else HBSA_LAUNCH_SM100_T(64, false); }
+#undef HBSA_LAUNCH_SM100_T
 #undef HBSA_LAUNCH_SM100
   if (e != cudaSuccess) { *err_text = cudaGetErrorString(e); return (int)e; }
   return 0;

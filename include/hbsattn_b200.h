@@ -185,6 +185,14 @@ int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
  * Applies to launches made after the call. */
 void hbsa_debug_set_wait_budget(long long clocks, int stall_producer);
 
+/* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes() bytes is
+ * set, four threads of the first CTA of every tensor-core attention launch (the MMA thread, one thread of each
+ * lane's softmax warps, one thread of the loader warp) write clock64() stamps of their pipeline events into
+ * it: four regions of 8192 int64, entry 0 of a region = number of stamps, every other entry = clock << 8 | event
+ * code.  NULL switches it off (the default); the kernel that runs then contains no stamp code. */
+size_t hbsa_debug_trace_bytes(void);
+void hbsa_debug_set_trace(void* device_buffer);
+
 /*
  * hbsa_forward for callers that cannot allocate: identical to hbsa_forward except that the
  * scratch memory is a fixed array inside the library instead of `args->workspace` (which is
