@@ -12,7 +12,18 @@ Bernoulli(0.1) with the diagonal block forced True, bf16, seed = rank.
 Metric: effective TFLOP/s over ACTIVE block pairs only: sum over active (kv-head, q-block, k-block)
 pairs of 4 * rows(qb) * rows(kb) * headdim, times the GQA group, divided by time.
 
-Printed by rank 0: one JSON line (see README / DESIGN.md for the fields).
+Rank 0 prints ONE JSON line.  Besides the contract fields (metric, value, ms_per_step, roofline, e2e,
+cpu_baseline, clocks, gpu_launches) it carries
+  sustained     the same step timed again for at least two seconds, with the SM clock sampled throughout
+  sharded       the long-context workload ("cfg4": batch 8 x 65536 tokens) split into (sample, kv-head) units over
+                the N ranks by longest-processing-time-first on active-pair FLOPs; strong scaling, no collective on the
+                data path, per-rank error statistics against the oracle gathered with one all_gather
+  gpu_baseline  the unmodified reference operator (Triton kernels, both tile modes) timed on the same GPU and inputs,
+                when baseline/_ref is installed (baseline/install_ref.py)
+
+--impl reference times the reference's CPU implementation of the path on the host cores: for --workload cfg1 (the
+reference's own CPU-runnable case) the UNMODIFIED reference from baseline/_ref, for the larger workloads the oracle
+port of it on (sample, kv-head) units (the unmodified causal code is a pure-Python loop over every (row, key) pair).
 """
 from __future__ import annotations
 
@@ -20,6 +31,7 @@ import argparse
 import ctypes
 import json
 import os
+import subprocess
 import sys
 import threading
 import time
@@ -33,6 +45,8 @@ if ROOT not in sys.path:
 
 WORKLOADS = {
     # name: batch, (q_lo, q_hi, q_round), k spec, nhead_q, nhead_k, headdim, qbs, kbs, causal, p_keep, force
+    "cfg1": dict(batch=5, q_lens=[32, 32, 32, 32, 32], k_lens=[32, 29, 39, 34, 23], hq=8, hk=2, d=32, qbs=32, kbs=16, causal=True,
+                 p=0.7, force=None, desc="batch 5 varlen (cu_q 0,32,..,160; cu_k 0,32,61,100,134,157), Hq8/Hk2, d32, 32x16 blocks, causal, mask p=0.7"),
     "cfg2": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
                  p=0.1, force="diag", desc="B8 x 8192 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.1 + diagonal"),
     "cfg2_b2": dict(batch=2, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
@@ -49,11 +63,12 @@ WORKLOADS = {
                  p=0.2, force="diag", desc="B16, q 128-512, k 16384-32768, Hq64/Hk8, d64, 16x128 blocks, bottom-right causal, mask p=0.2 + last valid"),
 }
 
-
-# DRAM bytes per launch of the attention kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
-# capture, profiles/fwd_sm100_kernel_cfg2.md): measured on the batch-2 cut of cfg2 (534.5 MB) and scaled by
-# the number of work items (x4 for batch 8; per-item statistics are identical).
+# DRAM bytes per launch of the attention kernel as one ncu capture measured them (dram__bytes_read.sum +
+# dram__bytes_write.sum of fwd_sm100_kernel on the batch-2 cut of cfg2: 536.0 MB), scaled by the number of work
+# items for the full workload (x4 for batch 8; per-item statistics are identical).  Workloads without a capture
+# report null and the compulsory bytes computed from the decision bitmap beside it.
 TRAFFIC_BYTES = {"cfg2_b2": 536.0e6, "cfg2": 4 * 536.0e6}
+
 
 # ----------------------------------------------------------------------------------------------
 # synthetic inputs
@@ -73,13 +88,16 @@ def host_block_tables(cu, bs):
 def make_workload(name, seed, device):
     w = WORKLOADS[name]
     rng = np.random.default_rng(seed)
-    lo, hi, rnd = w["q_len"]
-    q_lens = (rng.integers(lo, hi + 1, size=w["batch"]) // rnd) * rnd
-    if w["k_len"] == "same":
-        k_lens = q_lens.copy()
+    if "q_lens" in w:
+        q_lens, k_lens = np.asarray(w["q_lens"]), np.asarray(w["k_lens"])
     else:
-        klo, khi, krnd = w["k_len"]
-        k_lens = (rng.integers(klo, khi + 1, size=w["batch"]) // krnd) * krnd
+        lo, hi, rnd = w["q_len"]
+        q_lens = (rng.integers(lo, hi + 1, size=w["batch"]) // rnd) * rnd
+        if w["k_len"] == "same":
+            k_lens = q_lens.copy()
+        else:
+            klo, khi, krnd = w["k_len"]
+            k_lens = (rng.integers(klo, khi + 1, size=w["batch"]) // krnd) * krnd
     cu_q = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int64)
     cu_k = np.concatenate([[0], np.cumsum(k_lens)]).astype(np.int64)
     nqb, cnq, qb2b, rows_q = host_block_tables(cu_q, w["qbs"])
@@ -114,8 +132,22 @@ def active_flops(dec, rows_q, rows_k, headdim, group):
     return 4.0 * pairs_rows * headdim * group
 
 
+def compulsory_bytes(dec, wl):
+    """HBM bytes a forward cannot avoid: Q read and O written once, every K/V block that at least one active pair
+    touches read once, the mask bytes of in-sample (row, k-block) positions, the 64-byte work record per row."""
+    w = wl["w"]
+    touched = dec.any(dim=1).to(torch.float64)                                  # [Hk, NKB]
+    rk = torch.as_tensor(wl["rows_k"], dtype=torch.float64, device=dec.device)
+    kv = float((touched * rk[None, :]).sum().item()) * w["d"] * 2 * 2
+    qo = 2.0 * float(wl["cu_q"][-1]) * w["hq"] * w["d"] * 2
+    blocks_k = np.diff(wl["cnk"])
+    blocks_q = np.diff(wl["cnq"])
+    mask_bytes = float((blocks_q * blocks_k).sum()) * w["hk"]
+    return qo + kv + mask_bytes + 64.0 * w["hk"] * wl["nqb"]
+
+
 # ----------------------------------------------------------------------------------------------
-# clock sampling (read-only NVML)
+# clock sampling (read-only NVML) and placement
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
     REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
@@ -145,7 +177,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.01)
+            self._stop.wait(0.005)
 
     def __enter__(self):
         if self.nv is not None:
@@ -173,8 +205,49 @@ def physical_gpu_index(local):
     return local
 
 
+def bind_near_gpu(local):
+    """Pins this process to the CPU cores of the NUMA node its GPU hangs off (read-only look-up in sysfs), so that the
+    pinned staging buffers allocated afterwards live in that node's memory.  Returns what was done, for the record."""
+    try:
+        prop = torch.cuda.get_device_properties(local)
+        bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return {"numa_node": None, "note": "the platform reports no NUMA node for the GPU"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return {"numa_node": node, "cpus": len(allowed) or len(os.sched_getaffinity(0))}
+    except Exception as e:                                   # no sysfs, no permission: stay where the launcher put us
+        return {"numa_node": None, "note": f"{type(e).__name__}: {e}"[:120]}
+
+
+def copy_bandwidth(dev, nbytes=256 << 20):
+    """Host-to-device and device-to-host GB/s of this rank alone, pinned memory, one 256 MiB copy each way (best of 3)."""
+    h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
+        best = 0.0
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            b.synchronize()
+            best = max(best, nbytes / (a.elapsed_time(b) * 1e-3) / 1e9)
+        out[name] = best
+    return out
+
+
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle (a port of hbsattn/reference.py) on (sample, kv-head) slices of the workload
+# CPU arm: the reference's PyTorch code on the host cores
 # ----------------------------------------------------------------------------------------------
 def cpu_slice(wl, sample, hk):
     """CPU tensors of one independent (sample, kv-head) unit of the workload."""
@@ -212,20 +285,72 @@ def run_cpu_slices(wl, n_slices_max, budget_s, min_slices=1):
     return total_flops, total_s, done
 
 
-def reference_arm(args):
-    """The reference's CPU implementation of the path (its PyTorch code restated as the oracle port;
-    the unmodified Python reference cannot travel to the benchmark box), all host threads."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def use_host_cores():
     # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use the host cores it can get
     try:
         torch.set_num_threads(max(torch.get_num_threads(), min(len(os.sched_getaffinity(0)), 64)))
     except (AttributeError, OSError):
         pass
+    return torch.get_num_threads()
+
+
+def reference_line(args, value, secs_per_step, n, kind, cores, sample, w, extra=None):
+    line = {
+        "impl": "reference", "metric": "effective TFLOP/s over active block pairs, attention forward", "value": value,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": f"{args.workload}: {w['desc']}"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def reference_arm_unmodified(args):
+    """--workload cfg1: the unmodified reference (hbsattn_reference_v1_base and v3_qkallfirst from baseline/_ref) on CPU
+    tensors, one call per step."""
+    import baseline
+    from oracle import oracle_block_decisions
+    cores = use_host_cores()
     wl = make_workload(args.workload, 0, "cpu")
     w = wl["w"]
-    cores = torch.get_num_threads()
+    baseline.load_reference()
+    from hbsattn.reference import hbsattn_reference_v1_base, hbsattn_reference_v3_qkallfirst
+    from hbsattn.utils import calculate_blocks
+    mq = calculate_blocks(wl["cu_q_t"], w["qbs"])
+    mk = calculate_blocks(wl["cu_k_t"], w["kbs"])
+    call = (wl["q"], wl["k"], wl["v"], wl["cu_q_t"], wl["cu_k_t"], wl["mask"], w["qbs"], w["kbs"], w["causal"], None, *mq, *mk)
+    dec = oracle_block_decisions(wl["cu_q"], wl["cu_k"], wl["mask"], w["qbs"], w["kbs"], w["causal"])
+    flops = active_flops(torch.from_numpy(dec), wl["rows_q"], wl["rows_k"], w["d"], w["hq"] // w["hk"])
+    times = {}
+    for name, fn in (("v1_base", hbsattn_reference_v1_base), ("v3_qkallfirst", hbsattn_reference_v3_qkallfirst)):
+        for _ in range(max(1, args.warmup)):
+            fn(*call)
+        ts = []
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            fn(*call)
+            ts.append(time.perf_counter() - t0)
+        times[name] = {"median_s": float(np.median(ts)), "min_s": float(np.min(ts))}
+    best = min(t["median_s"] for t in times.values())
+    reference_line(args, flops / best / 1e12, best, args.steps, "reference", cores,
+                   f"the whole workload per step, unmodified hbsattn.reference on CPU tensors; per call {times}", w,
+                   {"reference_calls": times, "os_cpu_count": os.cpu_count()})
+
+
+def reference_arm(args):
+    """The reference's CPU implementation of the path, all host threads, on rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if args.workload == "cfg1":
+        import baseline
+        if baseline.reference_available():
+            return reference_arm_unmodified(args)
+    cores = use_host_cores()
+    wl = make_workload(args.workload, 0, "cpu")
+    w = wl["w"]
     for _ in range(args.warmup):
         run_cpu_slices(wl, 1, 0.0)
     flops, secs, n = 0.0, 0.0, 0
@@ -244,22 +369,182 @@ def reference_arm(args):
         secs += time.perf_counter() - t0
         flops += active_flops(torch.from_numpy(dec), rq, rk, w["d"], g)
         n += 1
-    value = flops / secs / 1e12
-    sample = f"{n} (sample, kv-head) units of {units} in the workload, one per step; {time.perf_counter() - t_all:.1f} s wall"
-    line = {
-        "impl": "reference", "metric": "effective TFLOP/s over active block pairs, attention forward", "value": value,
-        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": secs / max(n, 1) * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": f"{args.workload}: {w['desc']}"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line), flush=True)
+    sample = (f"{n} (sample, kv-head) units of {units} in the workload, one per step; {time.perf_counter() - t_all:.1f} s wall; "
+              "the port is a vectorised restatement, far faster than the reference's own pure-Python causal loop")
+    reference_line(args, flops / secs / 1e12, secs / max(n, 1), n, "port", cores, sample, w)
+
+
+def reference_gpu_arm(args):
+    """Internal (run as a child process by the GPU arm): the UNMODIFIED reference operator - its Triton kernels compiled by
+    this image's Triton - on the same workload, timed with the same CUDA-event loop.  Prints one JSON object."""
+    res = {}
+    try:
+        import baseline
+        ref = baseline.load_reference()
+        from hbsattn.utils import calculate_blocks
+        dev = torch.device("cuda", 0)
+        wl = make_workload(args.workload, 0, dev)
+        w = wl["w"]
+        mq = calculate_blocks(wl["cu_q_t"], w["qbs"])
+        mk = calculate_blocks(wl["cu_k_t"], w["kbs"])
+        pow2 = (w["qbs"] & (w["qbs"] - 1)) == 0 and (w["kbs"] & (w["kbs"] - 1)) == 0
+        for mode in ("auto", "fix") if pow2 else ("auto",):
+            try:
+                def call():
+                    return ref.HBSAttention(wl["q"], wl["k"], wl["v"], wl["cu_q_t"], wl["cu_k_t"], wl["mask"], w["qbs"], w["kbs"],
+                                            w["causal"], None, mode, *mq, *mk)
+                for _ in range(max(3, args.warmup)):          # the first call also runs Triton's autotuner
+                    call()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(args.steps):
+                    call()
+                b.record()
+                torch.cuda.synchronize()
+                res[mode] = {"ms_per_step": a.elapsed_time(b) / args.steps}
+            except Exception as e:
+                res[mode] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    except Exception as e:
+        res = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    print(json.dumps(res), flush=True)
 
 
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
+def sharded_leg(args, hb, lib, dev, rank, world, dist, peak):
+    """The long-context workload split into (sample, kv-head) units over the ranks.
+
+    Every unit (q, k, v of one sample and one kv-head with its q-heads, and its mask plane) is drawn from its own seed,
+    so any rank can generate any unit and no rank holds more than its share.  All ranks draw all mask planes (67 MB),
+    derive every unit's FLOPs over active pairs and the same longest-processing-time-first plan from them; a rank then
+    packs its units into one varlen problem with one kv-head and a CSR block mask and runs it as one call per step.
+    Time = max over ranks, work = sum over ranks: strong scaling of one fixed workload."""
+    from hbsattn_b200 import _lib
+    from hbsattn_b200.hbsa_interface import alloc_workspace, make_args, read_status
+    from hbsattn_b200.shard import active_plane, plan_imbalance, plan_units, plane_flops
+    from oracle import error_stats, oracle_block_decisions, oracle_forward
+
+    w = WORKLOADS[args.sharded_workload]
+    lo, hi, rnd = w["q_len"]
+    assert lo == hi and w["k_len"] == "same", "the sharded leg draws fixed-length units"
+    L, group, d, qbs, kbs = lo, w["hq"] // w["hk"], w["d"], w["qbs"], w["kbs"]
+    nqb, nkb = (L + qbs - 1) // qbs, (L + kbs - 1) // kbs
+    batch, hk = w["batch"], w["hk"]
+
+    def unit_mask(b, h):
+        g = torch.Generator(device=dev).manual_seed(1_000_003 * (b * hk + h) + 17)
+        m = torch.rand(nqb, nkb, generator=g, device=dev) < w["p"]
+        if w["force"] == "diag":
+            qi = torch.arange(nqb, device=dev)
+            m[qi, torch.clamp(((qi + 1) * qbs - 1) // kbs, max=nkb - 1)] = True
+        return active_plane(m, L, L, qbs, kbs, w["causal"])
+
+    flops = np.zeros((batch, hk))
+    planes = {}
+    for b in range(batch):
+        for h in range(hk):
+            planes[(b, h)] = unit_mask(b, h)
+            flops[b, h] = plane_flops(planes[(b, h)], L, L, qbs, kbs, d, group)
+    plan = plan_units(flops, world)
+    mine = plan[rank]
+    my_flops = float(sum(flops[b, h] for b, h in mine))
+
+    # ---- this rank's packed problem: one sample per unit, one kv-head, CSR rows over packed k-block indices
+    n_u = len(mine)
+    counts, cols = [], []
+    for i, u in enumerate(mine):
+        nz = planes[u].nonzero()
+        counts.append(torch.bincount(nz[:, 0], minlength=nqb))
+        cols.append((nz[:, 1] + i * nkb).to(torch.int32))
+    row_ptr = torch.zeros(n_u * nqb + 1, dtype=torch.int64, device=dev)
+    if n_u:
+        row_ptr[1:] = torch.cumsum(torch.cat(counts), 0)
+    col_idx = torch.cat(cols) if n_u else torch.zeros(0, dtype=torch.int32, device=dev)
+    row_ptr = row_ptr.to(torch.int32)
+    cu = torch.arange(n_u + 1, dtype=torch.int32, device=dev) * L
+    q = torch.empty(max(n_u, 1) * L, group, d, dtype=torch.bfloat16, device=dev)
+    k = torch.empty(max(n_u, 1) * L, 1, d, dtype=torch.bfloat16, device=dev)
+    v = torch.empty_like(k)
+    for i, (b, h) in enumerate(mine):
+        g = torch.Generator(device=dev).manual_seed(2_000_003 * (b * hk + h) + 29)
+        for t, heads in ((q, group), (k, 1), (v, 1)):
+            t[i * L:(i + 1) * L] = torch.randn(L, heads, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    del planes
+    out = torch.empty_like(q)
+    stream = torch.cuda.current_stream(dev)
+    ms, st = 0.0, {"max_abs": 0.0, "mean_abs": 0.0}
+    bad_rows = 0
+    steps = args.sharded_steps
+    if n_u:
+        ws = alloc_workspace(1, n_u * nqb, n_u * nkb, n_u, dev)
+        cargs = make_args(q, k, v, out, cu, cu, None, qbs, kbs, w["causal"], None, n_u * nqb, n_u * nkb, ws, _lib.HBSA_IMPL_AUTO,
+                          csr=(row_ptr, col_idx))
+
+        def step():
+            rc = lib.hbsa_build_schedule(ctypes.byref(cargs), stream.cuda_stream) or lib.hbsa_attention(ctypes.byref(cargs), stream.cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"hbsa call failed ({rc}): {_lib.last_error()}")
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        if read_status(ws)[0] != 0:
+            raise RuntimeError("device status after the sharded warm-up")
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    if n_u:
+        for _ in range(steps):
+            step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if n_u:
+        # ---- validation on this rank: the active-block counts of every row against the planes the plan was made from,
+        #      and one unit's output and decision bitmap against the oracle (fp32, on the GPU)
+        want_counts = (row_ptr[1:] - row_ptr[:-1]).to(torch.int32)
+        _, got_counts = hb.block_decisions_csr(q[:1], k[:1], cu, cu, row_ptr, col_idx, n_u * nqb, n_u * nkb, qbs, kbs, w["causal"],
+                                               want_bitmap=False)
+        bad_rows = int((got_counts.flatten() != want_counts).sum().item())
+        i = (rank * 7) % n_u
+        r0, r1 = int(row_ptr[i * nqb]), int(row_ptr[(i + 1) * nqb])
+        plane = torch.zeros(nqb, nkb, dtype=torch.bool, device=dev)
+        rows = torch.repeat_interleave(torch.arange(nqb, device=dev), want_counts[i * nqb:(i + 1) * nqb].long())
+        plane[rows, (col_idx[r0:r1] - i * nkb).long()] = True
+        gold = oracle_forward(q[i * L:(i + 1) * L].float(), k[i * L:(i + 1) * L].float(), v[i * L:(i + 1) * L].float(),
+                              [0, L], [0, L], plane[None], qbs, kbs, w["causal"], None)
+        st = error_stats(gold, out[i * L:(i + 1) * L])
+        del gold
+        want_dec = oracle_block_decisions([0, L], [0, L], plane[None].cpu(), qbs, kbs, w["causal"])
+        bad_rows += int((torch.from_numpy(want_dec[0]).to(dev) != plane).sum().item())   # the plan's own bitmap is the exact predicate
+    rec = torch.tensor([ms, my_flops, st["max_abs"], st["mean_abs"], float(bad_rows), float(n_u)], dtype=torch.float64, device=dev)
+    allrec = [torch.zeros_like(rec) for _ in range(world)]
+    if dist is not None:
+        dist.all_gather(allrec, rec)
+    else:
+        allrec = [rec]
+    rows = [[float(x) for x in r.tolist()] for r in allrec]
+    t_max = max(r[0] for r in rows)
+    total = sum(r[1] for r in rows)
+    value = total / (t_max * 1e-3) / 1e12
+    return {
+        "workload": f"{args.sharded_workload}: {w['desc']}", "scaling": "strong", "n_ranks": world, "units": batch * hk,
+        "partition": "(sample, kv-head) units, longest-processing-time-first on active-pair FLOPs; one packed CSR call per rank",
+        "plan_imbalance": plan_imbalance(plan, flops), "steps": steps, "ms_per_fwd": t_max, "value": value, "unit": "TFLOP/s",
+        "flop_per_fwd": total, "frac_of_peak_per_gpu": value / world / peak,
+        "per_rank": [{"ms": r[0], "tflops": r[1] / (r[0] * 1e-3) / 1e12 if r[0] > 0 else 0.0, "units": int(r[5]),
+                      "oracle_max_abs": r[2], "oracle_mean_abs": r[3], "decision_mismatches": int(r[4])} for r in rows],
+        "validated": all(r[2] <= 2e-2 and r[3] <= 1e-3 and r[4] == 0 for r in rows),
+        "collective": "none on the data path; NCCL all_gather of six numbers per rank for this record",
+    }
+
+
 def ours_arm(args):
     import hbsattn_b200 as hb
     from hbsattn_b200 import _lib
@@ -272,6 +557,7 @@ def ours_arm(args):
         raise RuntimeError("bench.py needs a CUDA device: hbsattn_b200 has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    placement = bind_near_gpu(local)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -288,6 +574,7 @@ def ours_arm(args):
     dec, counts = hb.block_decisions(q, k, cu_q_t, cu_k_t, mask, w["qbs"], w["kbs"], w["causal"])
     flops = active_flops(dec, wl["rows_q"], wl["rows_k"], w["d"], group)
     active_pairs = int(dec.sum().item())
+    must_bytes = compulsory_bytes(dec, wl)
     del dec
 
     stream = torch.cuda.current_stream(dev)
@@ -338,6 +625,21 @@ def ours_arm(args):
     if status[0] != 0:
         raise RuntimeError(f"device status {status[:4]} after the timed region")
 
+    # ---- the same step again for at least --sustained-seconds: what the kernel does once the power limit governs the clock
+    sus = None
+    if args.sustained_seconds > 0:
+        n_sus = max(args.steps, int(args.sustained_seconds * 1e3 / max(ms_total / args.steps, 1e-3)) + 1)
+        s_sampler = ClockSampler(physical_gpu_index(local))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with s_sampler:
+            s0.record(stream)
+            for _ in range(n_sus):
+                step()
+            s1.record(stream)
+            barrier()
+        sus = (s0.elapsed_time(s1) / n_sus, n_sus, s_sampler.summary())
+
     # ---- end to end through the operator API: pinned host buffers -> device -> HBSAttention -> host.
     # Every step copies its inputs in, builds the schedule, runs the kernel and copies the output out;
     # HostStagedAttention overlaps the copy out of step i with the copy in of step i + 1 (two device slots).
@@ -367,27 +669,42 @@ def ours_arm(args):
     hout = houts[0]
     h2d = sum(t.numel() * t.element_size() for t in (hq_, hk_, hv_, hmask, hcuq, hcuk))
     d2h = hout.numel() * hout.element_size()
+    link = copy_bandwidth(dev)             # this rank's copies alone, all ranks at the same time under torchrun
+    del hq_, hk_, hv_, hmask, houts, staged
 
     # ---- reduce over ranks: time = max, work = sum
-    red = torch.tensor([ms_total, kern_ms, e2e_ms], dtype=torch.float64, device=dev)
-    tot = torch.tensor([flops], dtype=torch.float64, device=dev)
+    red = torch.tensor([ms_total, kern_ms, e2e_ms, sus[0] if sus else 0.0, -link["h2d_gbs"], -link["d2h_gbs"]], dtype=torch.float64, device=dev)
+    tot = torch.tensor([flops, link["h2d_gbs"], link["d2h_gbs"]], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(red, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-    ms_total, kern_ms_max, e2e_ms = (float(x) for x in red.tolist())
-    flops_all = float(tot.item())
+    ms_total, kern_ms_max, e2e_ms, sus_ms, neg_h2d_min, neg_d2h_min = (float(x) for x in red.tolist())
+    flops_all, h2d_sum, d2h_sum = (float(x) for x in tot.tolist())
     ms_per_step = ms_total / args.steps
     value = flops_all / (ms_per_step * 1e-3) / 1e12
     e2e_value = flops_all / (e2e_ms / e2e_steps * 1e-3) / 1e12
 
-    if rank == 0:
-        peaks = {}
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    peak_sus = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    peak_kind = "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback 1590"
+
+    # ---- the long-context workload sharded over the ranks (frees the main workload's tensors first)
+    sharded = None
+    if args.sharded_workload != "none":
+        del q, k, v, out, mask, wl, cargs, ws
+        torch.cuda.empty_cache()
         try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        peak = float(peaks.get("bf16_tflops", 1590.0))
-        peak_kind = "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback 1590"
+            sharded = sharded_leg(args, hb, lib, dev, rank, world, dist, peak)
+        except Exception as e:
+            sharded = {"error": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+
+    if rank == 0:
         achieved = flops / (kern_ms * 1e-3) / 1e12          # rank 0's kernel on rank 0's work
         line = {
             "metric": "effective TFLOP/s over active block pairs, attention forward", "value": value, "unit": "TFLOP/s",
@@ -398,19 +715,54 @@ def ours_arm(args):
                        "l2": "q+k+v+o exceed the 126 MB L2; no flush", "kernel_family": {1: "generic", 2: "sm100"}.get(family, str(family)),
                        "step": "schedule build (3 small kernels) + attention kernel"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": TRAFFIC_BYTES.get(args.workload), "kernel": "fwd_sm100_kernel" if family == 2 else "fwd_generic_kernel",
+                         "traffic": TRAFFIC_BYTES.get(args.workload),
+                         "traffic_source": "one ncu capture of this kernel on the batch-2 cut, scaled by work items" if args.workload in TRAFFIC_BYTES else None,
+                         "compulsory_bytes": must_bytes, "hbm_gbs_at_compulsory": must_bytes / (kern_ms * 1e-3) / 1e9,
+                         "hbm_peak_gbs": peaks.get("hbm_gbs"),
+                         "kernel": "fwd_sm100_kernel" if family == 2 else "fwd_generic_kernel",
                          "kernel_ms": kern_ms, "peak_source": peak_kind},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                    "achieved_gbs_per_gpu": (h2d + d2h) / (e2e_ms / e2e_steps * 1e-3) / 1e9,
+                    "link_probe": {"h2d_gbs_sum": h2d_sum, "d2h_gbs_sum": d2h_sum, "h2d_gbs_min_rank": -neg_h2d_min,
+                                   "d2h_gbs_min_rank": -neg_d2h_min, "how": "256 MiB pinned copies, every rank at the same time"},
+                    "placement_rank0": placement},
             "gpu_launches": 4 * args.steps,
             "clocks": sampler.summary(),
         }
+        if sus:
+            s_clk = sus[2]
+            v_sus = flops_all / (sus_ms * 1e-3) / 1e12
+            line["sustained"] = {"steps": sus[1], "seconds": sus_ms * sus[1] / 1e3, "ms_per_step": sus_ms, "value": v_sus, "unit": "TFLOP/s",
+                                 "clocks": s_clk, "frac_of_sustained_peak": v_sus / world / peak_sus, "sustained_peak": peak_sus,
+                                 "ms_per_step_at_max_clock": (sus_ms * s_clk["sm_mhz"] / s_clk["sm_max_mhz"]) if s_clk.get("sm_mhz") and s_clk.get("sm_max_mhz") else None}
+            line["roofline"]["frac_sustained"] = v_sus / world / peak_sus
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
             torch.cuda.synchronize()
-            cores = torch.get_num_threads()
-            cf, cs, n = run_cpu_slices(wl, w["batch"] * w["hk"], args.cpu_budget)
+            cores = use_host_cores()
+            wl_cpu = make_workload(args.workload, rank, dev)
+            cf, cs, n = run_cpu_slices(wl_cpu, w["batch"] * w["hk"], args.cpu_budget)
+            del wl_cpu
             line["cpu_baseline"] = {"value": cf / cs / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                    "sample": f"{n} (sample, kv-head) units of {w['batch'] * w['hk']} in the workload, {cs:.1f} s of oracle time"}
+                                    "sample": f"{n} (sample, kv-head) units of {w['batch'] * w['hk']} in the workload, {cs:.1f} s of oracle time; "
+                                              "the port is a vectorised restatement, far faster than the reference's own pure-Python causal loop"}
+        if world == 1 and not args.no_gpu_baseline:
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            try:
+                res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference_gpu", "--workload", args.workload,
+                                      "--steps", str(min(args.steps, 20)), "--warmup", "3"], capture_output=True, text=True, timeout=600)
+                gb = json.loads(res.stdout.strip().splitlines()[-1]) if res.stdout.strip() else {"unavailable": res.stderr[-300:]}
+            except Exception as e:
+                gb = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+            for mode in ("auto", "fix"):
+                if isinstance(gb.get(mode), dict) and "ms_per_step" in gb[mode]:
+                    gb[mode]["tflops"] = flops / (gb[mode]["ms_per_step"] * 1e-3) / 1e12
+                    gb[mode]["ours_speedup"] = gb[mode]["ms_per_step"] / ms_per_step
+            gb["what"] = "unmodified reference HBSAttention (Triton kernels compiled by this image's Triton), same workload, seed 0, CUDA events"
+            line["gpu_baseline"] = gb
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -422,15 +774,22 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of oracle time for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the second, clock-sampled timed loop (0: skip)")
+    ap.add_argument("--sharded-workload", default="cfg4", choices=["cfg4", "cfg4_16k", "none"],
+                    help="fixed-length workload for the strong-scaling record")
+    ap.add_argument("--sharded-steps", type=int, default=5)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         reference_arm(args)
+    elif args.impl == "reference_gpu":
+        reference_gpu_arm(args)
     else:
         ours_arm(args)
 

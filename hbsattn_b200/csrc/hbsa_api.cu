@@ -162,10 +162,11 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   hbsa::Problem p;
   int rc = make_problem(args, false, &p);
   if (rc != 0) return rc;
-  if (!decisions) return fail(HBSA_ERR_NULL, "decisions must not be NULL");
+  if (!decisions && !counts) return fail(HBSA_ERR_NULL, "decisions and counts must not both be NULL");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   hbsa::Workspace ws = hbsa::make_workspace(args->workspace, p.nhead_k, p.num_q_block, p.num_k_block, p.batch);
-  cudaError_t e = cudaMemsetAsync(decisions, 0, (size_t)p.nhead_k * p.num_q_block * p.num_k_block, stream);
+  cudaError_t e = cudaSuccess;
+  if (decisions) e = cudaMemsetAsync(decisions, 0, (size_t)p.nhead_k * p.num_q_block * p.num_k_block, stream);
   if (e != cudaSuccess) return fail_cuda(e, "hbsa_block_decisions (memset)");
   e = hbsa::launch_schedule(p, ws, decisions, stream);
   if (e != cudaSuccess) return fail_cuda(e, "hbsa_block_decisions");

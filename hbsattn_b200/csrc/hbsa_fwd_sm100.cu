@@ -6,46 +6,42 @@
 //  * A work item is one 128-row M tile of one (kv-head, q-block): `TT = 128 / GP` tokens times
 //    `GP` q-heads of the GQA group packed into the MMA M dimension, so that one K/V tile fetch
 //    serves GP heads (the reference runs one program per q-head and re-reads K/V per head).
-//  * One persistent CTA per SM works on TWO independent items at a time ("lanes" A and B), each with
-//    its own Q tile, its own S and O accumulators in TMEM and its own four softmax warps.  While the
-//    softmax warps of one lane turn S into P, the tensor pipe runs the products of the other lane,
-//    so the two latency chains S -> softmax -> P V interleave on one tensor pipe that a single thread
-//    feeds in a fixed order.  Items come from an atomic cursor over the ItemRecord table the schedule
-//    kernels wrote.
+//  * Persistent CTAs, two per SM, pull work items from an atomic cursor over the ItemRecord table the
+//    schedule kernels wrote; the producer warp publishes each item to the other warps through a
+//    two-slot ring in shared memory and runs ahead of them.  Two CTAs per SM mean two independent
+//    items in flight, so the start and the end of one item hide behind the tiles of the other.
 //  * Only mask-active k-blocks are touched: the producer warp compacts the mask row with warp
-//    ballots and issues TMA loads of exactly those K/V tiles (up to 128 rows each) into one ring of
-//    shared-memory slots that both lanes share, in the order the MMA thread consumes them (the
-//    reference loops over all k-blocks of the sample and polls the mask byte,
+//    ballots and issues TMA loads of exactly those K/V tiles (at most 64 rows each) into two-stage K
+//    and V rings (the reference loops over all k-blocks of the sample and polls the mask byte,
 //    fwd_triton_fix_tile_size.py:117-124).
-//  * S = Q K^T is one M128 x N<=128 tcgen05.mma chain per K tile; O += P V is issued in two groups of
-//    up to 64 keys, so the first group runs while the softmax warps are still in the exponentials of
-//    the second 64 columns.  P (in the input dtype, as at fwd_triton_fix_tile_size.py:187) is written
-//    back into TMEM over S columns that were already read and consumed as the A operand of the
-//    second MMA, so it never touches shared memory.  Because tcgen05.mma instructions of one thread
-//    execute in issue order, S(t+1) of a lane is issued right behind P V(t) into the columns P(t)
-//    occupies without waiting for P V(t) to complete (HBSA_STRICT_TCGEN05 builds wait and fence
-//    instead; they exist to check this ordering).
-//  * Online softmax in registers, one thread per row, 64 columns at a time: in-place -inf masking on
-//    diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles and no
-//    shared-memory exchange.  The exponentials run against the reference maximum of the previous
-//    columns; whether that reference is stale is read off the packed P itself, and only then is the
-//    running output rescaled in TMEM and the 64 columns redone exactly from registers.
-//  * The last CTA to leave rewinds the work cursor, so one schedule serves any number of launches.
-//    With `lse` set, ln sum exp of every row goes out beside O.
+//  * S = Q K^T and O += P V are tcgen05.mma instructions with fp32 accumulators in TMEM.  S is
+//    double-buffered, so S(t+1) is computed while the softmax warps work on S(t); P (in the input
+//    dtype, as at fwd_triton_fix_tile_size.py:187) is written back into TMEM over the S columns it
+//    came from and consumed as the A operand of the second MMA, so it never touches shared memory.
+//    One thread issues every MMA; because tcgen05.mma instructions of one thread execute in issue
+//    order, S(t+2) is issued right behind P V(t) into the buffer that P(t) occupies without waiting
+//    for P V(t) to complete (HBSA_STRICT_TCGEN05 builds wait and fence instead; they exist to check this
+//    ordering bit for bit).
+//  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
+//    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
+//    and no shared-memory exchange.  The exponentials of a tile run against the reference maximum of the
+//    previous tiles while the tile's own maximum is computed alongside; the running output is rescaled in
+//    TMEM (and the tile redone) only when a row maximum grows by more than 2^8.  The arithmetic around the
+//    exponentials is two-wide (fma/add/mul.rn.f32x2).
+//  * The last CTA to leave rewinds the work cursor, so one schedule serves any number of launches.  With
+//    `lse` set, ln sum exp of every row goes out beside O.
 //
-// Warp roles (320 threads): warps 0-3 softmax + epilogue of lane A, warps 4-7 of lane B (TMEM lane
-// quarter = warp id % 4), warp 8 TMEM allocator + MMA issuer, warp 9 work fetch + TMA producer.
-// TMEM (512 columns): S_A [0,128), S_B [128,256), O_A [256,256+D), O_B [256+D,256+2D).
+// Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp id), warp 4 work
+// fetch + TMA producer, warp 5 TMEM allocator + MMA issuer.  TMEM (256 columns): S0 [0,64), S1 [64,128),
+// O [128,256).
 //
-// mbarriers.  Per lane: T counts K/V tiles, I published items, Iq those of them that have tiles.  A waiter
-// for the c-th completion of a barrier uses parity c & 1, which is only sound while the barrier is at most one
-// completion ahead of what the waiter looks for.  That holds for every single-entry barrier below because its
-// waiter observes each completion before the next one can happen; barriers whose waiters look only now and
-// then (item_*, pv_done) are two-entry arrays indexed by the low bit of the count, with parity (count >> 1) & 1.
-//   ring_full / ring_empty [slot]: TMA bytes landed / the product that read the slot is done
-//   s_full [lane]: S = Q K^T done                   p_full [lane][half]: P of 64 columns written
-//   pv_done [lane][half][2]: O += P V of the half done   q_full / q_free [lane]: Q landed / last S of the item done
-//   o_free [lane]: epilogue has read O out of TMEM  item_full / item_done [lane][2]: item slot written / left
+// mbarriers.  T counts K/V tiles over the whole life of the CTA, I counts published items, Iq those
+// of them that have tiles.  Two-entry barrier arrays are indexed by the low bit of the count and
+// complete once per use, so a waiter for count c uses entry c & 1 and parity (c >> 1) & 1:
+//   k_full / v_full [T]: TMA bytes landed          s_full [T]: S = Q K^T done (K stage free again)
+//   p_full [T]: P written (one arrival per warp)   pv_done [T]: O += P V done (V stage free again)
+//   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O out of TMEM
+//   item_full [I]: item slot written               item_done [I]: all consumers left item I
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
@@ -60,20 +56,15 @@ namespace hbsa {
 
 namespace {
 
-constexpr int kThreads = 320;
-constexpr int kLaneWarps = 4;         // softmax warps per lane
-constexpr int kMmaWarp = 8;
-constexpr int kProducerWarp = 9;
-constexpr int kTileRowsMax = 128;     // rows of a K/V tile
-constexpr int kSubCols = 64;          // columns the softmax handles at a time
-constexpr int kTmemCols = 512;
-constexpr uint32_t kTmemSStride = 128u;
-constexpr uint32_t kTmemOBase = 256u;
-constexpr int kMaxSlots = 8;          // K/V ring
-constexpr int kMinSlots = 4;
-constexpr int kTileInfo = 8;          // per-lane ring of tile start columns
+constexpr int kThreads = 192;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kTileRowsMax = 64;      // rows of a K/V tile
+constexpr int kTmemCols = 256;
+constexpr uint32_t kSStride = 64u;    // TMEM columns between the two S buffers
+constexpr uint32_t kTmemOCol = 128u;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
-constexpr size_t kSmemLimit = 232448; // dynamic shared memory a CTA may opt into on sm_100
 
 struct Sm100Params {
   Problem p;
@@ -82,7 +73,7 @@ struct Sm100Params {
   long long o_s0, o_s1;        // elements
   float* lse;                  // NULL or [total_q, nhead_q]: natural-log sum of exponentials per row
   int total_q;
-  int nt;                      // rows of one K/V tile (multiple of 16, <= 128)
+  int nt;                      // rows of one K/V tile (multiple of 16, <= 64)
   int n_sub;                   // K/V tiles per k-block
   int gp, gp_shift;            // q-heads packed into one M tile
   int n_head_sub;              // group / gp
@@ -90,40 +81,21 @@ struct Sm100Params {
   int tiles_per_qblock;
   int items_per_row;           // n_head_sub * tiles_per_qblock
   long long total_items;       // rows * items_per_row
-  int n_slots;                 // K/V ring slots
-  uint32_t slot_bytes;
-  int o_vec32;                 // output rows are 32-byte aligned: 256-bit stores
-  int debug_stall;             // debugging aid: the producer publishes nothing, every wait runs out
   float scale_log2;
   long long wait_budget;       // clock64 ticks
+  int debug_stall;             // debugging aid: the producer publishes nothing, every wait runs out
   long long* trace;            // debugging aid: clock64 stamps of CTA 0 (NULL in normal use)
 };
 
-// Debugging aid.  While a trace buffer is set, four threads of CTA 0 (the MMA thread, the first thread of each
-// lane's softmax warps, the first thread of the producer warp) write (clock64 << 8 | code) stamps of their
-// pipeline events into their own region of kTraceCap entries; entry 0 of a region holds the number of stamps.
-// The shipped instantiation carries no stamp code at all.
-constexpr int kTraceCap = 8192;
-constexpr int kTraceRegions = 4;
-template <bool TRACE>
-struct Tracer {
-  long long* base;
-  int n;
-  __device__ __forceinline__ void init(long long* buf, int region, bool mine) {
-    base = (TRACE && buf != nullptr && mine && blockIdx.x == 0) ? buf + (size_t)region * kTraceCap : nullptr;
-    n = 1;
-  }
-  __device__ __forceinline__ void put(int code) {
-    if (TRACE) {
-      if (base != nullptr && n < kTraceCap) base[n++] = (clock64() << 8) | (long long)code;
-    }
-  }
-  __device__ __forceinline__ void done() {
-    if (TRACE) {
-      if (base != nullptr) base[0] = n - 1;
-    }
-  }
-};
+constexpr int kTraceTiles = 96;      // tiles of CTA 0 that are stamped
+constexpr int kTraceSlots = 32;      // stamps per tile
+constexpr int kTraceCtas = 512;      // behind the tile stamps: start time (ns) and SM of the first CTAs
+// slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV(t) issue starts, 5 PV(t) issued,
+// 6 softmax sees S, 7 row max done, 8 P written, 9 P arrival done, 10 item start, 11 epilogue done,
+// 12 S in registers, 13 epilogue starts, 22 last PV seen complete, 23 O in registers
+__device__ __forceinline__ void stamp(long long* trace, int tile, int slot) {
+  if (trace != nullptr && blockIdx.x == 0 && tile >= 0 && tile < kTraceTiles) trace[tile * kTraceSlots + slot] = clock64();
+}
 
 // What the producer tells the other warps about one work item.
 struct ItemSlot {
@@ -138,40 +110,21 @@ struct ItemSlot {
 };
 
 struct __align__(16) Control {
-  unsigned long long ring_full[kMaxSlots], ring_empty[kMaxSlots];
-  unsigned long long item_full[2][2], item_done[2][2];
-  unsigned long long q_full[2], q_free[2], s_full[2], p_full[2][2], pv_done[2][2][2], o_free[2];
+  unsigned long long item_full[2], item_done[2];
+  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], o_free[2];
   unsigned long long drain;
   uint32_t tmem_base;
   int abort_flag;
-  int tile_k0[2][kTileInfo];
-  ItemSlot slot[2][2];
+  int tile_k0[4];
+  ItemSlot slot[2];
+  uint4 stage[kSoftmaxWarps][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
 };
-
-// Compile-time tuning knobs of the softmax threads (see exp16):
-//   HBSA_POLY_PAIRS  of every 8 column pairs, how many take their exponentials from a polynomial on the FMA pipe
-//                    instead of the exp unit (0..8); only bf16/fp16 tiles without masked columns use it
-//   HBSA_ALU_PACK    1: fp32 -> bf16 pairs are packed with integer adds and a byte permute instead of cvt
-#ifndef HBSA_POLY_PAIRS
-#define HBSA_POLY_PAIRS 0
-#endif
-#ifndef HBSA_ALU_PACK
-#define HBSA_ALU_PACK 0
-#endif
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   uint32_t r;
   if (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
-}
-// P >= 0 and finite-or-inf: rounding to bf16 is "add half an ulp of the kept part, keep the upper 16 bits" (ties go
-// up instead of to even, one ulp apart once in 2^16 values).  The conversion instruction shares the exp unit, which is
-// the pipe the softmax threads saturate; these three run on the integer pipe.
-template <bool BF16> __device__ __forceinline__ uint32_t pack2_p(float lo, float hi) {
-  if (BF16 && HBSA_ALU_PACK)
-    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
-  return pack2<BF16>(lo, hi);
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -192,55 +145,21 @@ __device__ __forceinline__ void max16(const uint32_t* r, float (&mx)[4]) {
   mx[2] = max3(mx[2], __uint_as_float(r[12]), __uint_as_float(r[13]));
   mx[3] = max3(mx[3], __uint_as_float(r[14]), __uint_as_float(r[15]));
 }
-// 2^x for two values by polynomial on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f from a
-// cubic (relative error 7.5e-5, far below the 2^-9 of the 16-bit P it is rounded to); n goes straight into the
-// exponent field.  x is clamped to [-126, 255]: below, the result is a tiny normal number; above 128 the exponent
-// overflows into a bit pattern that, read as an unsigned 16-bit float, is larger than any legal P - exactly what
-// the staleness check of the caller looks for.
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
-  float x0, x1;
-  ptx::unpack_f32x2(x2, x0, x1);
-  x0 = fminf(fmaxf(x0, -126.f), 255.f);
-  x1 = fminf(fmaxf(x1, -126.f), 255.f);
-  const uint64_t xc = ptx::pack_f32x2(x0, x1);
-  const uint64_t magic = ptx::pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23: the sum's low mantissa bits are round(x)
-  const uint64_t t = ptx::add_f32x2(xc, magic);
-  const uint64_t n = ptx::add_f32x2(t, ptx::pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f = ptx::fma_f32x2(n, ptx::pack_f32x2(-1.f, -1.f), xc);
-  uint64_t q = ptx::fma_f32x2(f, ptx::pack_f32x2(0.05517164617776871f, 0.05517164617776871f), ptx::pack_f32x2(0.2426111251115799f, 0.2426111251115799f));
-  q = ptx::fma_f32x2(q, f, ptx::pack_f32x2(0.6932609677314758f, 0.6932609677314758f));
-  q = ptx::fma_f32x2(q, f, ptx::pack_f32x2(0.9999280571937561f, 0.9999280571937561f));
-  float q0, q1, t0, t1;
-  ptx::unpack_f32x2(q, q0, q1);
-  ptx::unpack_f32x2(t, t0, t1);
-  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-}
-
 // P = exp2(S * scale - m) for 16 columns, packed to 16-bit pairs; four independent partial row sums.
-// The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe time, half the
-// issue slots.  POLY of the 8 column pairs take the polynomial (callers pass 0 for tiles with masked columns:
-// -inf must come out as an exact zero).
-template <bool BF16, int POLY>
+// The scale-and-shift and the sums use the two-wide fp32 instructions: same FMA-pipe time, half the issue
+// slots.
+template <bool BF16>
 __device__ __forceinline__ void exp16(const uint32_t* r, uint32_t (&pk)[8], float scale_log2, float neg_m, float (&sum)[4]) {
   const uint64_t scale2 = ptx::pack_f32x2(scale_log2, scale_log2), neg_m2 = ptx::pack_f32x2(neg_m, neg_m);
   uint64_t sa = ptx::pack_f32x2(sum[0], sum[2]), sb = ptx::pack_f32x2(sum[1], sum[3]);
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const int q = i >> 1;
-    const uint64_t x2 = ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2);
-    float p0, p1;
-    if (((q + 1) * POLY) / 8 > (q * POLY) / 8) {
-      exp2_poly2(x2, p0, p1);
-    } else {
-      float x0, x1;
-      ptx::unpack_f32x2(x2, x0, x1);
-      p0 = ptx::ex2_approx(x0);
-      p1 = ptx::ex2_approx(x1);
-    }
-    if (q & 1) sb = ptx::add_f32x2(sb, ptx::pack_f32x2(p0, p1));
+    float x0, x1;
+    ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_b32x2(r[i], r[i + 1]), scale2, neg_m2), x0, x1);
+    const float p0 = ptx::ex2_approx(x0), p1 = ptx::ex2_approx(x1);
+    if ((i >> 1) & 1) sb = ptx::add_f32x2(sb, ptx::pack_f32x2(p0, p1));
     else sa = ptx::add_f32x2(sa, ptx::pack_f32x2(p0, p1));
-    pk[q] = pack2_p<BF16>(p0, p1);
+    pk[i >> 1] = pack2<BF16>(p0, p1);
   }
   ptx::unpack_f32x2(sa, sum[0], sum[2]);
   ptx::unpack_f32x2(sb, sum[1], sum[3]);
@@ -253,62 +172,59 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // Barrier entry and parity for the c-th use of a two-entry barrier array.
-__device__ __forceinline__ uint32_t bar2(uint32_t base, int c) { return base + 8u * (uint32_t)(c & 1); }
-__device__ __forceinline__ uint32_t par2(int c) { return (uint32_t)(c >> 1) & 1u; }
+__device__ __forceinline__ uint32_t bar_of(uint32_t base, int c) { return base + 8u * (uint32_t)(c & 1); }
+__device__ __forceinline__ uint32_t par_of(int c) { return (uint32_t)(c >> 1) & 1u; }
 
-// pv_done barrier of (lane, half of the tile) for the lane's tile number T, and the parity to wait for.
-__device__ __forceinline__ uint32_t pv_bar(uint32_t base, int L, int h, int T) { return base + 32u * (uint32_t)L + 16u * (uint32_t)h + 8u * (uint32_t)(T & 1); }
-__device__ __forceinline__ uint32_t pv_par(int T) { return (uint32_t)(T >> 1) & 1u; }
-
-// Position in the K/V ring: slot index and the parity of its current use.
-struct RingPos {
-  int slot;
-  uint32_t phase;
-  __device__ __forceinline__ void advance(int n_slots) {
-    if (++slot == n_slots) { slot = 0; phase ^= 1u; }
+// The issue sequences of the MMA thread.  Every descriptor and TMEM address is precomputed into
+// registers once per CTA, so a product is nothing but back-to-back tcgen05.mma instructions.
+template <int KSTEPS>
+__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[8], const uint64_t (&kd)[8], uint32_t idesc) {
+  ptx::mma_ss_c<false>(tS, qd[0], kd[0], idesc);
+#pragma unroll
+  for (int ks = 1; ks < KSTEPS; ++ks) ptx::mma_ss_c<true>(tS, qd[ks], kd[ks], idesc);
+}
+// N k-steps of O (+)= P V; the first one overwrites O when `first`.
+template <int N>
+__device__ __forceinline__ void issue_pv_n(uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
+  if (first) ptx::mma_ts_c<false>(tO, pa[0], vd[0], idesc);
+  else ptx::mma_ts_c<true>(tO, pa[0], vd[0], idesc);
+#pragma unroll
+  for (int ks = 1; ks < N; ++ks) ptx::mma_ts_c<true>(tO, pa[ks], vd[ks], idesc);
+}
+__device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa)[4], const uint64_t (&vd)[4], uint32_t idesc, bool first) {
+  switch (n) {
+    case 1: issue_pv_n<1>(tO, pa, vd, idesc, first); break;
+    case 2: issue_pv_n<2>(tO, pa, vd, idesc, first); break;
+    case 3: issue_pv_n<3>(tO, pa, vd, idesc, first); break;
+    default: issue_pv_n<4>(tO, pa, vd, idesc, first); break;
   }
-};
+}
 
-// Per-lane state of the producer warp (all values warp-uniform except bit_next).
-struct ProdLane {
-  bool done, pend_v;
-  int pend_tok;              // global token of the first row of the tile whose V is still to be loaded
-  int hk;
-  int tiles_left;
-  const uint8_t* mrow;       // dense mask: mask row of the item, at the sample's first k-block
-  const int32_t* cidx;       // CSR mask: the row's first active entry
-  int n_reach, k_begin, k_len, kb0;
-  int n_src;                 // entries to scan: causal-reachable k-blocks (dense) or active entries (CSR)
-  int base;                  // first entry of the 32-entry chunk `bal` describes
-  uint32_t bal;              // active blocks of the chunk not handed out yet
-  bool bit_next;             // dense: this lane's mask byte of the chunk after `base`
-  int val_cur, val_next;     // CSR: this lane's in-sample k-block index of the chunk at / after `base`
-  int blk, sub;              // block being handed out and its next sub-tile
-  int I, Iq, T;              // items published, items with tiles, tiles loaded
-};
-
-// Per-lane state of the MMA thread.
-struct MmaLane {
-  bool done, pend, pend_first, pend_last, first;
-  int pend_item, pend_T;
-  int tiles_left;
-  int I, Iq, Ipv, T;         // items seen, items whose first S / first P V was issued, tiles
-};
-
+// TRACE = true is the instantiation that runs while a debug trace buffer is set; the shipped path carries
+// no stamp code at all.
 template <int D, bool BF16, bool TRACE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
   using namespace ptx;
   constexpr int PANELS = D / 64;
   constexpr uint32_t Q_BYTES = 128u * D * 2u;
+  constexpr uint32_t KV_BYTES_MAX = (uint32_t)kTileRowsMax * D * 2u;
   const Problem& p = P.p;
-
   using OutT = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
   OutT* const o_base = static_cast<OutT*>(P.o);
+
   if (P.ws.status[0] != HBSA_STATUS_OK) {
     zero_fill_output(o_base, P.o_s0, P.o_s1, 1ll, P.total_q, p.nhead_q, D, P.lse);
     return;
+  }
+  if (TRACE && P.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceCtas) {
+    unsigned long long ns;
+    uint32_t smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    P.trace[kTraceTiles * kTraceSlots + blockIdx.x] = (long long)ns;
+    P.trace[kTraceTiles * kTraceSlots + kTraceCtas + blockIdx.x] = (long long)smid;
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -318,35 +234,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = ((raw_addr + 1023u) & ~1023u) - raw_addr;
   uint8_t* const smem = smem_raw + pad;
-  const uint32_t sQ = raw_addr + pad;                 // 2 lanes
-  const uint32_t sRing = sQ + 2u * Q_BYTES;           // n_slots slots
-  Control* const ctl = reinterpret_cast<Control*>(smem + 2u * Q_BYTES + (uint32_t)P.n_slots * P.slot_bytes);
-  const uint32_t bar_ring_full = smem_u32(&ctl->ring_full[0]), bar_ring_empty = smem_u32(&ctl->ring_empty[0]);
-  const uint32_t bar_item_full = smem_u32(&ctl->item_full[0][0]), bar_item_done = smem_u32(&ctl->item_done[0][0]);
-  const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_q_free = smem_u32(&ctl->q_free[0]);
-  const uint32_t bar_s_full = smem_u32(&ctl->s_full[0]), bar_p_full = smem_u32(&ctl->p_full[0][0]);
-  const uint32_t bar_pv_done = smem_u32(&ctl->pv_done[0][0][0]), bar_o_free = smem_u32(&ctl->o_free[0]);
-  const uint32_t bar_drain = smem_u32(&ctl->drain);
+  const uint32_t sQ = raw_addr + pad;
+  const uint32_t sK = sQ + Q_BYTES;                   // 2 stages
+  const uint32_t sV = sK + 2 * KV_BYTES_MAX;          // 2 stages
+  Control* const ctl = reinterpret_cast<Control*>(smem + Q_BYTES + 4 * KV_BYTES_MAX);
+  const uint32_t bar_item_full = smem_u32(&ctl->item_full[0]), bar_item_done = smem_u32(&ctl->item_done[0]);
+  const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
+  const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
+  const uint32_t bar_p_full = smem_u32(&ctl->p_full[0]), bar_pv_done = smem_u32(&ctl->pv_done[0]);
+  const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]);
   volatile int* const abort_flag = &ctl->abort_flag;
+  volatile int* const tile_k0 = ctl->tile_k0;
+  volatile ItemSlot* const slots = ctl->slot;
 
   if (tid == 0) {
-    for (int i = 0; i < kMaxSlots; ++i) {
-      mbar_init(bar_ring_full + 8 * i, 1);
-      mbar_init(bar_ring_empty + 8 * i, 1);
-    }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(bar_item_full + 8 * i, 1);
-      mbar_init(bar_item_done + 8 * i, kLaneWarps + 1);         // softmax warps of the lane + the MMA thread
-      mbar_init(bar_p_full + 8 * i, kLaneWarps);
-    }
-    for (int i = 0; i < 8; ++i) mbar_init(bar_pv_done + 8 * i, 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_item_full + 8 * i, 1);
+      mbar_init(bar_item_done + 8 * i, kSoftmaxWarps + 1);      // softmax warps + the MMA thread
       mbar_init(bar_q_full + 8 * i, 1);
-      mbar_init(bar_q_free + 8 * i, 1);
+      mbar_init(bar_k_full + 8 * i, 1);
+      mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_o_free + 8 * i, kLaneWarps);
+      mbar_init(bar_p_full + 8 * i, kSoftmaxWarps);
+      mbar_init(bar_pv_done + 8 * i, 1);
+      mbar_init(bar_o_free + 8 * i, kSoftmaxWarps);
     }
-    mbar_init(bar_drain, 1);
+    mbar_init(smem_u32(&ctl->drain), 1);
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
@@ -366,560 +279,461 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const long long budget = P.wait_budget;
   const uint32_t kv_tile_bytes = (uint32_t)P.nt * D * 2u;
   const uint32_t kv_panel_bytes = (uint32_t)P.nt * 128u;
-  const int nt0 = P.nt < kSubCols ? P.nt : kSubCols;       // columns of the first / second half of a tile
-  const int nt1 = P.nt - nt0;
 
   if (warp == kProducerWarp) {
     // =============================== work fetch + TMA producer ===============================
-    // Walks the same fixed order as the MMA thread: lanes alternate; a turn of a lane loads V of the tile
-    // whose K went out at the lane's previous turn, then K of the lane's next tile (fetching the next work
-    // item first when the current one has no tile left).
     const ItemRecord* const records = reinterpret_cast<const ItemRecord*>(P.ws.items);
     unsigned long long* const cursor = reinterpret_cast<unsigned long long*>(P.ws.cursor);
-    ProdLane st[2];
-#pragma unroll
-    for (int L = 0; L < 2; ++L) {
-      st[L].done = false; st[L].pend_v = false; st[L].pend_tok = 0; st[L].hk = 0; st[L].tiles_left = 0;
-      st[L].mrow = p.mask; st[L].cidx = p.csr_idx; st[L].n_reach = 0; st[L].k_begin = 0; st[L].k_len = 0; st[L].kb0 = 0;
-      st[L].n_src = 0; st[L].base = 0; st[L].bal = 0u; st[L].bit_next = false; st[L].val_cur = 0; st[L].val_next = 0;
-      st[L].blk = -1; st[L].sub = 0; st[L].I = 0; st[L].Iq = 0; st[L].T = 0;
-    }
-    RingPos rp = {0, 0u};
-    Tracer<TRACE> tr;
-    tr.init(P.trace, 3, lane == 0);
-    const bool csr = p.csr_ptr != nullptr;
+    int I = 0, Iq = 0, T = 0;
     bool ok = P.debug_stall == 0;
-    // Two claims ahead: the record of the candidate item is on its way while the current items run, and the
-    // atomic of the one after it is in flight.
-    long long cand_idx = 0, next_idx = 0;
-    if (lane == 0) {
-      cand_idx = (long long)atomicAdd(cursor, 1ull);
-      next_idx = (long long)atomicAdd(cursor, 1ull);
-    }
-    cand_idx = __shfl_sync(0xffffffffu, cand_idx, 0);
+    // one fetch ahead: the atomic and the record load of the next item overlap the current item
+    long long next_idx = 0;
+    if (lane == 0) next_idx = (long long)atomicAdd(cursor, 1ull);
     next_idx = __shfl_sync(0xffffffffu, next_idx, 0);
-    ItemRecord cand_rec = {};
-    if (cand_idx < P.total_items) cand_rec = records[cand_idx / P.items_per_row];
-    // The first 32 mask entries of the candidate's row are requested one turn after its record, so that neither load
-    // is waited for when a lane takes the candidate.
-    bool cand_bits_req = false, cand_bit = false;
-    int cand_val = 0;
-    auto request_cand_bits = [&]() {
-      if (csr) {
-        cand_val = lane < cand_rec.count ? p.csr_idx[cand_rec.csr_begin + lane] - cand_rec.kb0 : 0;
-      } else {
-        const uint8_t* mrow = p.mask + cand_rec.hk * p.mask_s0 + cand_rec.qb * p.mask_s1 + (long long)cand_rec.kb0 * p.mask_s2;
-        cand_bit = lane < cand_rec.n_reach && mrow[(long long)lane * p.mask_s2] != 0;
+    while (ok) {
+      const long long idx = next_idx;
+      const bool have = idx < P.total_items;
+      ItemRecord rec = {};
+      int rem = 0;
+      if (have) {
+        rec = records[idx / P.items_per_row];
+        rem = (int)(idx % P.items_per_row);
+        if (lane == 0) next_idx = (long long)atomicAdd(cursor, 1ull);
+        next_idx = __shfl_sync(0xffffffffu, next_idx, 0);
       }
-      cand_bits_req = true;
-    };
+      const int hsub = rem / P.tiles_per_qblock, qt = rem % P.tiles_per_qblock;
+      const int tile_tok0 = rec.q_begin + qt * P.tt;
+      if (have && tile_tok0 >= rec.q_end) continue;          // M tile past the ragged end of the q-block
+      const int head0 = rec.hk * p.group + hsub * P.gp;
+      const int n_tiles = have ? rec.n_tiles : -1;
 
-    auto acquire = [&]() -> bool {                       // the ring slot at rp is free again
-      return warp_wait(bar_ring_empty + 8u * (uint32_t)rp.slot, rp.phase ^ 1u, abort_flag, budget);
-    };
-
-    auto turn = [&](ProdLane& s, const int L) {
-      if (!cand_bits_req && cand_idx < P.total_items) request_cand_bits();
-      if (s.pend_v) {
-        if (!acquire()) { ok = false; return; }
-        if (lane == 0) {
-          const uint32_t bar = bar_ring_full + 8u * (uint32_t)rp.slot;
-          const uint32_t dst = sRing + (uint32_t)rp.slot * P.slot_bytes;
-          mbar_arrive_expect_tx(bar, kv_tile_bytes);
-#pragma unroll
-          for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(dst + pn * kv_panel_bytes, &tm_v, bar, pn * 64, s.hk, s.pend_tok);
-        }
-        rp.advance(P.n_slots);
-        s.pend_v = false;
-        tr.put(0x10 + L);
-      }
-      if (s.done) return;
-      while (s.tiles_left == 0) {
-        // ---- next work item of this lane
-        const long long idx = cand_idx;
-        const bool have = idx < P.total_items;
-        if (have && !cand_bits_req) request_cand_bits();
-        const ItemRecord rec = cand_rec;
-        const bool rec_bit = cand_bit;
-        const int rec_val = cand_val;
-        const int rem = have ? (int)(idx % P.items_per_row) : 0;
-        cand_idx = next_idx;
-        cand_bits_req = false;
-        if (have) {
-          if (cand_idx < P.total_items) cand_rec = records[cand_idx / P.items_per_row];
-          if (lane == 0) next_idx = (long long)atomicAdd(cursor, 1ull);
-          next_idx = __shfl_sync(0xffffffffu, next_idx, 0);
-        }
-        const int hsub = rem / P.tiles_per_qblock, qt = rem % P.tiles_per_qblock;
-        const int tile_tok0 = rec.q_begin + qt * P.tt;
-        if (have && tile_tok0 >= rec.q_end) continue;          // M tile past the ragged end of the q-block
-        const int head0 = rec.hk * p.group + hsub * P.gp;
-        const int n_tiles = have ? rec.n_tiles : -1;
-        // publish: slot I & 1 of the lane is free once every consumer has left item I - 2
-        if (s.I >= 2 && !warp_wait(bar2(bar_item_done + 16u * L, s.I), par2(s.I - 2), abort_flag, budget)) { ok = false; return; }
-        if (lane == 0) {
-          volatile ItemSlot* sl = &ctl->slot[L][s.I & 1];
-          sl->n_tiles = n_tiles;
-          sl->tile_tok0 = tile_tok0;
-          sl->head0 = head0;
-          sl->q_end = rec.q_end;
-          sl->qi0 = rec.q_in0 + qt * P.tt;
-          sl->k_len = rec.k_len;
-          sl->off = rec.off;
-          __threadfence_block();
-          mbar_arrive(bar2(bar_item_full + 16u * L, s.I));
-        }
-        ++s.I;
-        tr.put(0x20 + L);
-        if (!have) { s.done = true; return; }
-        if (n_tiles <= 0) continue;
-        // Q of the lane has one buffer: the last S of the lane's previous item must be done
-        if (s.Iq >= 1 && !warp_wait(bar_q_free + 8u * L, (uint32_t)(s.Iq - 1) & 1u, abort_flag, budget)) { ok = false; return; }
-        if (lane == 0) {
-          const uint32_t bar = bar_q_full + 8u * L;
-          mbar_arrive_expect_tx(bar, Q_BYTES);
-#pragma unroll
-          for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(sQ + (uint32_t)L * Q_BYTES + pn * (128u * 128u), &tm_q, bar, pn * 64, head0, tile_tok0);
-        }
-        ++s.Iq;
-        tr.put(0x30 + L);
-        s.hk = rec.hk;
-        s.tiles_left = n_tiles;
-        s.n_reach = rec.n_reach;
-        s.k_begin = rec.k_begin;
-        s.k_len = rec.k_len;
-        s.kb0 = rec.kb0;
-        s.base = -32;
-        s.bal = 0u;
-        s.blk = -1;
-        s.sub = 0;
-        if (csr) {
-          s.cidx = p.csr_idx + rec.csr_begin;
-          s.n_src = rec.count;
-          s.val_next = rec_val;
-        } else {
-          s.mrow = p.mask + rec.hk * p.mask_s0 + rec.qb * p.mask_s1 + (long long)rec.kb0 * p.mask_s2;
-          s.n_src = rec.n_reach;
-          s.bit_next = rec_bit;
-        }
-      }
-      // ---- first row (in-sample) of the lane's next active K/V tile
-      int k0 = -1;
-      while (true) {
-        if (s.blk >= 0 && s.sub < P.n_sub) {
-          k0 = s.blk * p.kbs + s.sub * P.nt;
-          if (k0 < s.k_len) { ++s.sub; break; }
-        }
-        while (s.bal == 0u) {                                  // next chunk of 32 entries; they were requested a chunk ago
-          s.base += 32;
-          const int jn = s.base + 32 + lane;
-          if (csr) {
-            const int n = s.n_src - s.base;
-            s.bal = n >= 32 ? 0xffffffffu : (n > 0 ? (1u << n) - 1u : 0u);
-            s.val_cur = s.val_next;
-            s.val_next = jn < s.n_src ? s.cidx[jn] - s.kb0 : 0;
-          } else {
-            s.bal = __ballot_sync(0xffffffffu, s.bit_next);
-            s.bit_next = jn < s.n_src && s.mrow[(long long)jn * p.mask_s2] != 0;
-          }
-          if (s.base >= s.n_src) { s.bal = 0u; break; }         // cannot happen while tiles are left; keeps the loop finite
-        }
-        if (s.bal == 0u) { ok = false; if (lane == 0) *abort_flag = 1; return; }
-        const int pos = __ffs(s.bal) - 1;
-        s.bal &= s.bal - 1;
-        s.blk = csr ? __shfl_sync(0xffffffffu, s.val_cur, pos) : s.base + pos;
-        s.sub = 0;
-      }
-      if (!acquire()) { ok = false; return; }
-      if (lane == 0) {
-        ctl->tile_k0[L][s.T & (kTileInfo - 1)] = k0;
-        __threadfence_block();
-        const uint32_t bar = bar_ring_full + 8u * (uint32_t)rp.slot;
-        const uint32_t dst = sRing + (uint32_t)rp.slot * P.slot_bytes;
-        mbar_arrive_expect_tx(bar, kv_tile_bytes);
-#pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(dst + pn * kv_panel_bytes, &tm_k, bar, pn * 64, s.hk, s.k_begin + k0);
-      }
-      rp.advance(P.n_slots);
-      tr.put(0x40 + L);
-      s.pend_v = true;
-      s.pend_tok = s.k_begin + k0;
-      ++s.T;
-      --s.tiles_left;
-    };
-
-    while (ok && !(st[0].done && st[1].done && !st[0].pend_v && !st[1].pend_v)) {
-      turn(st[0], 0);
+      // publish: slot I & 1 is free once every consumer has left item I - 2
+      if (I >= 2) ok = warp_wait(bar_of(bar_item_done, I), par_of(I - 2), abort_flag, budget);
       if (!ok) break;
-      turn(st[1], 1);
+      if (lane == 0) {
+        volatile ItemSlot* sl = &slots[I & 1];
+        sl->n_tiles = n_tiles;
+        sl->tile_tok0 = tile_tok0;
+        sl->head0 = head0;
+        sl->q_end = rec.q_end;
+        sl->qi0 = rec.q_in0 + qt * P.tt;
+        sl->k_len = rec.k_len;
+        sl->off = rec.off;
+        __threadfence_block();
+        mbar_arrive(bar_of(bar_item_full, I));
+      }
+      ++I;
+      if (!have) break;
+      if (n_tiles <= 0) continue;
+
+      // Q has one buffer: the previous item's last S (tile T-1) must be done.  S products complete in
+      // order, so this covers tile T-2 (whose K stage the first tile of this item reuses) as well.
+      if (T >= 1) ok = warp_wait(bar_of(bar_s_full, T - 1), par_of(T - 1), abort_flag, budget);
+      if (!ok) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar_of(bar_q_full, Iq), Q_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn)
+          tma_load_3d(sQ + pn * (128u * 128u), &tm_q, bar_of(bar_q_full, Iq), pn * 64, head0, tile_tok0);
+      }
+      ++Iq;
+      // Active k-blocks of the row, 32 entries at a time and one chunk ahead: bytes of the dense mask row (a warp
+      // ballot compacts them), or the entries of the row's CSR list (in-sample block indices, already compact).
+      const bool csr = p.csr_ptr != nullptr;
+      const int n_src = csr ? rec.count : rec.n_reach;
+      const uint8_t* mrow = csr ? nullptr : p.mask + rec.hk * p.mask_s0 + rec.qb * p.mask_s1 + (long long)rec.kb0 * p.mask_s2;
+      const int32_t* cidx = csr ? p.csr_idx + rec.csr_begin : nullptr;
+      bool bit_next = false;
+      int val_next = 0;
+      if (csr) val_next = lane < n_src ? cidx[lane] - rec.kb0 : 0;
+      else bit_next = lane < n_src && mrow[(long long)lane * p.mask_s2] != 0;
+      for (int base = 0; base < n_src && ok; base += 32) {
+        uint32_t bal;
+        const int val_cur = val_next;
+        {                                                   // entries of the next chunk, one chunk ahead
+          const int jn = base + 32 + lane;
+          if (csr) {
+            const int n = n_src - base;
+            bal = n >= 32 ? 0xffffffffu : (1u << n) - 1u;
+            val_next = jn < n_src ? cidx[jn] - rec.kb0 : 0;
+          } else {
+            bal = __ballot_sync(0xffffffffu, bit_next);
+            bit_next = jn < n_src && mrow[(long long)jn * p.mask_s2] != 0;
+          }
+        }
+        while (bal != 0 && ok) {
+          const int pos = __ffs(bal) - 1;
+          bal &= bal - 1;
+          const int jj = csr ? __shfl_sync(0xffffffffu, val_cur, pos) : base + pos;
+          const int blk_k0 = jj * p.kbs;
+          for (int sub = 0; sub < P.n_sub && ok; ++sub) {
+            const int k0 = blk_k0 + sub * P.nt;
+            if (k0 >= rec.k_len) break;
+            if (T >= 2) ok = warp_wait(bar_of(bar_s_full, T), par_of(T - 2), abort_flag, budget);
+            if (!ok) break;
+            if (lane == 0) {
+              tile_k0[T & 3] = k0;
+              __threadfence_block();
+              mbar_arrive_expect_tx(bar_of(bar_k_full, T), kv_tile_bytes);
+#pragma unroll
+              for (int pn = 0; pn < PANELS; ++pn)
+                tma_load_3d(sK + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_k, bar_of(bar_k_full, T), pn * 64, rec.hk, rec.k_begin + k0);
+              if (TRACE) stamp(P.trace, T, 0);
+            }
+            // V stage T & 1 is free once the P V product of tile T-2 is done
+            if (T >= 2) ok = warp_wait(bar_of(bar_pv_done, T), par_of(T - 2), abort_flag, budget);
+            if (!ok) break;
+            if (lane == 0) {
+              mbar_arrive_expect_tx(bar_of(bar_v_full, T), kv_tile_bytes);
+#pragma unroll
+              for (int pn = 0; pn < PANELS; ++pn)
+                tma_load_3d(sV + (T & 1) * KV_BYTES_MAX + pn * kv_panel_bytes, &tm_v, bar_of(bar_v_full, T), pn * 64, rec.hk, rec.k_begin + k0);
+              if (TRACE) stamp(P.trace, T, 1);
+            }
+            ++T;
+          }
+        }
+      }
     }
-    tr.done();
-    // Copies that were issued are always waited for by the MMA thread (it gives up only on barriers
-    // of its own sequence), and the CTA does not retire before that thread is through.
+    if (!ok) {
+      // Gave up: let the copies already issued land before the CTA retires (bounded).
+      for (int back = 1; back <= 2 && T - back >= 0; ++back) {
+        mbar_wait_bounded(bar_of(bar_k_full, T - back), par_of(T - back), abort_flag, budget >> 4);
+        mbar_wait_bounded(bar_of(bar_v_full, T - back), par_of(T - back), abort_flag, budget >> 4);
+      }
+    }
   } else if (warp == kMmaWarp) {
     // =============================== MMA issuer ===============================
-    // One thread issues every tcgen05.mma of the CTA.  Lanes alternate; a turn of a lane issues P V of the
-    // lane's tile in flight (two groups of up to 64 keys, each as soon as its P is there) and then S of the
-    // lane's next tile.  S(t+1) goes into the columns P(t) occupies: instructions of one thread execute in
-    // issue order, so P V(t) has read P(t) before S(t+1) writes.
+    // One thread issues every tcgen05.mma of the CTA in the order S(0), S(1), PV(0), S(2), PV(1), S(3), ...
+    // S(t+2) goes into the buffer that P(t) occupies and is issued right behind PV(t) without waiting for
+    // PV(t) to complete: instructions of one thread execute in issue order, so PV(t) has read P(t) before
+    // S(t+2) writes.  The thread polls with non-blocking probes and issues whichever of "next P V" / "next
+    // S" has its inputs ready; a clock budget bounds the loop.
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(BF16, false, false, 128, P.nt);
       const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
+      const int ksteps = P.nt >> 4;
       const uint32_t desc_hi = smem_desc_hi(1024u);
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
-      const uint32_t slot_units = P.slot_bytes >> 4;
       // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
       // V is MN-major: 16 keys further = 2048 bytes = 128 units.  P: 8 TMEM columns per 16 keys.
-      uint64_t qd[2][D / 16];
-      uint32_t koff[D / 16];
+      uint64_t qd[8], kd0[8], kd1[8], vd0[4], vd1[4];
+      uint32_t pa0[4], pa1[4];
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
         const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
-        qd[0][ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
-        qd[1][ks] = smem_desc_join(smem_desc_lo(sQ + Q_BYTES, 16u) + qo, desc_hi);
-        koff[ks] = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
+        qd[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
+        kd0[ks] = smem_desc_join(smem_desc_lo(sK, 16u) + ko, desc_hi);
+        kd1[ks] = smem_desc_join(smem_desc_lo(sK + KV_BYTES_MAX, 16u) + ko, desc_hi);
       }
-      const uint32_t k_lo0 = smem_desc_lo(sRing, 16u);
-      const uint32_t v_lo0 = smem_desc_lo(sRing, kv_panel_bytes);
-      const int ks0 = nt0 >> 4, ks1 = nt1 >> 4;
-      MmaLane ml[2];
 #pragma unroll
-      for (int L = 0; L < 2; ++L) {
-        ml[L].done = false; ml[L].pend = false; ml[L].pend_first = false; ml[L].pend_last = false; ml[L].first = false;
-        ml[L].pend_item = 0; ml[L].pend_T = 0; ml[L].tiles_left = 0;
-        ml[L].I = 0; ml[L].Iq = 0; ml[L].Ipv = 0; ml[L].T = 0;
+      for (int ks = 0; ks < 4; ++ks) {
+        vd0[ks] = smem_desc_join(smem_desc_lo(sV, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        vd1[ks] = smem_desc_join(smem_desc_lo(sV + KV_BYTES_MAX, kv_panel_bytes) + (uint32_t)ks * 128u, desc_hi);
+        pa0[ks] = tmem_base + (uint32_t)ks * 8u;
+        pa1[ks] = tmem_base + kSStride + (uint32_t)ks * 8u;
       }
-      RingPos rc = {0, 0u};
-      Tracer<TRACE> tr;
-      tr.init(P.trace, 0, true);
-      bool ok = true;
-      auto wait = [&](uint32_t bar, uint32_t parity) -> bool {
-        const bool r = mbar_wait_bounded(bar, parity, abort_flag, budget);
-#ifdef HBSA_STRICT_TCGEN05
-        tc_fence_after();
-#endif
-        return r;
-      };
-
-      auto turn = [&](MmaLane& s, const int L) {
-        const uint32_t tS = tmem_base + (uint32_t)L * kTmemSStride;
-        const uint32_t tO = tmem_base + kTmemOBase + (uint32_t)L * D;
-        if (s.pend) {
-          // ---- O (+)= P V of the lane's tile in flight; its V tile is the next ring entry
-          tr.put(0x10 + L);
-          if (!wait(bar_ring_full + 8u * (uint32_t)rc.slot, rc.phase)) { ok = false; return; }
-          tr.put(0x20 + L);
-          // the first P V of an item overwrites O: the epilogue of the lane's previous item must have read it
-          if (s.pend_first && s.Ipv >= 1 && !wait(bar_o_free + 8u * L, (uint32_t)(s.Ipv - 1) & 1u)) { ok = false; return; }
-          const uint32_t v_lo = v_lo0 + (uint32_t)rc.slot * slot_units;
-          const uint32_t par = (uint32_t)s.pend_T & 1u;
-          if (!wait(bar_p_full + 16u * L, par)) { ok = false; return; }
-          tr.put(0x30 + L);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            if (ks < ks0) mma_ts(tO, tS + (uint32_t)ks * 8u, smem_desc_join(v_lo + (uint32_t)ks * 128u, desc_hi), idesc_pv,
-                                 (s.pend_first && ks == 0) ? 0u : 1u);
-          tc_commit(pv_bar(bar_pv_done, L, 0, s.pend_T));
-          tr.put(0x40 + L);
-          if (ks1 > 0) {
-            if (!wait(bar_p_full + 16u * L + 8u, par)) { ok = false; return; }
-            tr.put(0x50 + L);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              if (ks < ks1) mma_ts(tO, tS + 32u + (uint32_t)ks * 8u, smem_desc_join(v_lo + (uint32_t)(4 + ks) * 128u, desc_hi), idesc_pv, 1u);
-            tc_commit(pv_bar(bar_pv_done, L, 1, s.pend_T));
+      const uint32_t tO = tmem_base + kTmemOCol;
+      // S side: item qI (count of published items), its tiles left, number of items with tiles so far, next tile
+      int qI = 0, q_left = 0, qIq = 0, qT = 0;
+      bool q_have = false, q_first = false, finished = false;
+      // P V side: the items whose tiles are in flight, per tile "first of its item" / "last of its item"
+      int pT = 0;                    // next tile to issue P V for (pT <= qT <= pT + 2)
+      int pIq = 0;                   // items with tiles whose first P V has been issued
+      int fl_first[2] = {0, 0}, fl_last[2] = {0, 0}, fl_item[2] = {0, 0};   // indexed by tile & 1
+      long long t_progress = clock64();
+      while (true) {
+        bool progress = false;
+        if (!q_have && !finished && mbar_test(bar_of(bar_item_full, qI), par_of(qI))) {
+          const int n_tiles = slots[qI & 1].n_tiles;
+          if (n_tiles < 0) {
+            finished = true;
+          } else if (n_tiles == 0) {
+            mbar_arrive(bar_of(bar_item_done, qI));
+            ++qI;
+          } else {
+            q_have = true;
+            q_first = true;
+            q_left = n_tiles;
           }
-          tc_commit(bar_ring_empty + 8u * (uint32_t)rc.slot);
-          tr.put(0x60 + L);
-          rc.advance(P.n_slots);
-          if (s.pend_first) ++s.Ipv;
-          if (s.pend_last) mbar_arrive(bar2(bar_item_done + 16u * L, s.pend_item));   // through with the item
-          s.pend = false;
+          progress = true;
         }
-        if (s.done) return;
-        while (s.tiles_left == 0) {
-          if (!wait(bar2(bar_item_full + 16u * L, s.I), par2(s.I))) { ok = false; return; }
-          const int n_tiles = ctl->slot[L][s.I & 1].n_tiles;
-          if (n_tiles < 0) { s.done = true; return; }
-          if (n_tiles == 0) {
-            mbar_arrive(bar2(bar_item_done + 16u * L, s.I));
-            ++s.I;
-            continue;
-          }
-          s.tiles_left = n_tiles;
-          s.first = true;
-        }
-        // ---- S = Q K^T of the lane's next tile; its K tile is the next ring entry
-        tr.put(0x70 + L);
-        if (!wait(bar_ring_full + 8u * (uint32_t)rc.slot, rc.phase)) { ok = false; return; }
-        tr.put(0x80 + L);
-        if (s.first && !wait(bar_q_full + 8u * L, (uint32_t)s.Iq & 1u)) { ok = false; return; }
-        tr.put(0x90 + L);
+        if (pT < qT) {
+          bool ready = mbar_test(bar_of(bar_p_full, pT), par_of(pT)) && mbar_test(bar_of(bar_v_full, pT), par_of(pT));
+          // the first P V of an item overwrites O: the epilogue of the previous item must have read it
+          if (ready && fl_first[pT & 1] && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
+          if (ready) {
+            // No tcgen05.fence::after_thread_sync here in the shipped build: P(t) is complete in TMEM before
+            // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip was
+            // observed.  HBSA_STRICT_TCGEN05 builds execute the fence; the two builds must agree bit for bit.
 #ifdef HBSA_STRICT_TCGEN05
-        // every P V group of the lane has completed before S overwrites the columns of P
-        if (s.T >= 1 && !wait(pv_bar(bar_pv_done, L, ks1 > 0 ? 1 : 0, s.T - 1), pv_par(s.T - 1))) { ok = false; return; }
+            tc_fence_after();
 #endif
-        const uint32_t k_lo = k_lo0 + (uint32_t)rc.slot * slot_units;
-        if (L == 0) {
-          mma_ss_c<false>(tS, qd[0][0], smem_desc_join(k_lo + koff[0], desc_hi), idesc_qk);
-#pragma unroll
-          for (int ks = 1; ks < D / 16; ++ks) mma_ss_c<true>(tS, qd[0][ks], smem_desc_join(k_lo + koff[ks], desc_hi), idesc_qk);
+            if (TRACE) stamp(P.trace, pT, 4);
+            if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
+            else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
+            tc_commit(bar_of(bar_pv_done, pT));
+            if (TRACE) stamp(P.trace, pT, 5);
+            if (fl_first[pT & 1]) ++pIq;
+            if (fl_last[pT & 1]) mbar_arrive(bar_of(bar_item_done, fl_item[pT & 1]));   // through with the item
+            ++pT;
+            progress = true;
+          }
+        }
+        if (q_have && qT < pT + 2) {
+          bool ready = mbar_test(bar_of(bar_k_full, qT), par_of(qT));
+          if (ready && q_first) ready = mbar_test(bar_of(bar_q_full, qIq), par_of(qIq));
+#ifdef HBSA_STRICT_TCGEN05
+          // S(t) overwrites the columns of P(t-2): wait until P V(t-2) has completed instead of relying on the
+          // issue order of this thread, and fence after every observation
+          if (ready && qT >= 2) ready = mbar_test(bar_of(bar_pv_done, qT - 2), par_of(qT - 2));
+          if (ready) tc_fence_after();
+#endif
+          if (ready) {
+            if (TRACE) stamp(P.trace, qT, 2);
+            const uint32_t tSb = tmem_base + (uint32_t)(qT & 1) * kSStride;
+            if (qT & 1) issue_qk<D / 16>(tSb, qd, kd1, idesc_qk);
+            else issue_qk<D / 16>(tSb, qd, kd0, idesc_qk);
+            tc_commit(bar_of(bar_s_full, qT));
+            if (TRACE) stamp(P.trace, qT, 3);
+            fl_first[qT & 1] = q_first ? 1 : 0;
+            fl_last[qT & 1] = q_left == 1 ? 1 : 0;
+            fl_item[qT & 1] = qI;
+            ++qT;
+            if (q_first) ++qIq;
+            q_first = false;
+            if (--q_left == 0) {
+              ++qI;
+              q_have = false;
+            }
+            progress = true;
+          }
+        }
+        if (finished && pT == qT) break;
+        if (progress) {
+          t_progress = clock64();
         } else {
-          mma_ss_c<false>(tS, qd[1][0], smem_desc_join(k_lo + koff[0], desc_hi), idesc_qk);
-#pragma unroll
-          for (int ks = 1; ks < D / 16; ++ks) mma_ss_c<true>(tS, qd[1][ks], smem_desc_join(k_lo + koff[ks], desc_hi), idesc_qk);
+          if (*abort_flag) break;
+          if (clock64() - t_progress > budget) { *abort_flag = 1; break; }
         }
-        tc_commit(bar_s_full + 8u * L);
-        tc_commit(bar_ring_empty + 8u * (uint32_t)rc.slot);
-        if (s.tiles_left == 1) tc_commit(bar_q_free + 8u * L);             // the lane's Q buffer may be refilled
-        tr.put(0xa0 + L);
-        rc.advance(P.n_slots);
-        s.pend = true;
-        s.pend_first = s.first;
-        s.pend_last = s.tiles_left == 1;
-        s.pend_item = s.I;
-        s.pend_T = s.T;
-        ++s.T;
-        if (s.first) { ++s.Iq; s.first = false; }
-        if (--s.tiles_left == 0) ++s.I;
-      };
-
-      while (ok && !(ml[0].done && ml[1].done && !ml[0].pend && !ml[1].pend)) {
-        turn(ml[0], 0);
-        if (!ok) break;
-        turn(ml[1], 1);
       }
-      tr.done();
-      // Every product issued so far has completed before the CTA gives TMEM back (bounded).
-      tc_commit(bar_drain);
-      mbar_wait_bounded(bar_drain, 0u, abort_flag, budget);
+      // Whatever this thread has issued completes before the CTA gives its tensor memory back, also when it gave up
+      // (bounded by the clock alone: the abort flag is already set then).
+      tc_commit(smem_u32(&ctl->drain));
+      mbar_wait_clock(smem_u32(&ctl->drain), 0u, budget);
     }
     __syncwarp();
   } else {
     // =============================== softmax + epilogue ===============================
-    const int L = warp >> 2, wq = warp & 3;
-    const int row = wq * 32 + lane;                  // 0..127: row of the M tile = TMEM lane
-    const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
-    const uint32_t tSlane = tmem_base + (uint32_t)L * kTmemSStride + lane_off;
-    const uint32_t tOmine = tmem_base + kTmemOBase + (uint32_t)L * D + lane_off;
+    const int row = tid;                             // 0..127: row of the M tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const int my_nc = P.nt;                          // columns of a tile: 16, 32, 48 or 64
+    const uint32_t tOmine = tmem_base + kTmemOCol + lane_off;
     const float scale_log2 = P.scale_log2;
-    const int n_half = nt1 > 0 ? 2 : 1;
-    Tracer<TRACE> tr;
-    tr.init(P.trace, 1 + L, wq == 0 && lane == 0);
-    int I = 0, T = 0;
+    int I = 0, Iq = 0, T = 0;
     bool ok = true;
     while (ok) {
-      ok = warp_wait(bar2(bar_item_full + 16u * L, I), par2(I), abort_flag, budget);
+      ok = warp_wait(bar_of(bar_item_full, I), par_of(I), abort_flag, budget);
       if (!ok) break;
-      const volatile ItemSlot* sl = &ctl->slot[L][I & 1];
-      const int n_tiles = sl->n_tiles;
+      const int n_tiles = slots[I & 1].n_tiles;
       if (n_tiles < 0) break;
-      tr.put(0x10);
-      const int tile_tok0 = sl->tile_tok0, head0 = sl->head0, q_end = sl->q_end;
-      const int r_tok = tile_tok0 + (row >> P.gp_shift), r_head = head0 + (row & (P.gp - 1));
+      const int tile_tok0 = slots[I & 1].tile_tok0, head0 = slots[I & 1].head0, q_end = slots[I & 1].q_end;
       if (n_tiles == 0) {
         // No active k-block: the rows are exact zeros (fwd_triton_fix_tile_size.py:189).
+        const int r_tok = tile_tok0 + (row >> P.gp_shift);
         if (r_tok < q_end) {
-          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + r_head * P.o_s1);
+          uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
 #pragma unroll
           for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
-          if (P.lse != nullptr) P.lse[(long long)r_tok * p.nhead_q + r_head] = -INFINITY;
+          if (P.lse != nullptr) P.lse[(long long)r_tok * p.nhead_q + head0 + (row & (P.gp - 1))] = -INFINITY;
         }
       } else {
-        int limit_row = sl->k_len - 1;
-        if (p.causal) limit_row = min(limit_row, sl->qi0 + (row >> P.gp_shift) + sl->off);
+        int limit_row = slots[I & 1].k_len - 1;
+        if (p.causal) limit_row = min(limit_row, slots[I & 1].qi0 + (row >> P.gp_shift) + slots[I & 1].off);
         float m_ref = -INFINITY, l = 0.f;
+        if (TRACE && tid == 0) stamp(P.trace, T, 10);
         for (int t = 0; t < n_tiles && ok; ++t, ++T) {
-          ok = warp_wait(bar_s_full + 8u * L, (uint32_t)T & 1u, abort_flag, budget);
+          ok = warp_wait(bar_of(bar_s_full, T), par_of(T), abort_flag, budget);
           if (!ok) break;
           tc_fence_after();
-          tr.put(0x20);
-          const int tile_col0 = ctl->tile_k0[L][T & (kTileInfo - 1)];
-          for (int h = 0; h < n_half && ok; ++h) {
-            const int my_nc = h == 0 ? nt0 : nt1;                          // columns of this half: 16, 32, 48 or 64
-            const int col_limit = limit_row - tile_col0 - h * kSubCols;    // columns <= col_limit are valid
-            const uint32_t tSmine = tSlane + (uint32_t)h * kSubCols;       // S of this half
-            const uint32_t tPmine = tSlane + (uint32_t)h * (kSubCols / 2); // P of this half (16-bit pairs)
-            // on the causal diagonal or at the ragged end of the sample; decided per warp, because the two code paths
-            // below both contain warp-wide TMEM stores (rows that are not on the edge mask nothing)
-            const bool edge = __any_sync(0xffffffffu, col_limit < my_nc - 1);
-            // ---- this thread's row of S of this half, all in registers before its first P is stored (P of the second
-            //      half lands on S columns of the first half, which are in registers by then).  Load and wait stay in
-            //      one straight piece of code: the registers of an asynchronous TMEM load must not be moved by the
-            //      compiler before the wait.
-            uint32_t r[64];
+          if (TRACE && tid == 0) stamp(P.trace, T, 6);
+          const int col_limit = limit_row - tile_k0[T & 3];            // tile columns <= col_limit are valid
+          const uint32_t tSmine = tmem_base + (uint32_t)(T & 1) * kSStride + lane_off;
+
+          // ---- this thread's row of S, all in registers.  The first 16 columns are awaited alone so that
+          //      work on them overlaps the TMEM latency of the rest.
+          uint32_t r[64];
+          const bool edge = col_limit < my_nc - 1;      // tile on the causal diagonal or at the ragged end of the sample
+          tmem_ld16(tSmine, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+          tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
-            tmem_wait_ld();
-            if (h == 0) tr.put(0x21);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pmax0 = 0u, pmax1 = 0u;
-            bool exact = t == 0 && h == 0;                 // first columns of the item: the maximum must come first
-            if (!exact) {
-              // Optimistic pass: exponentials against the reference maximum of the previous columns (any
-              // reference gives the same softmax; it only has to keep P in range).  If a P turns out to
-              // exceed 2^8, the exact pass below redoes these columns.
-              const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
-              if (edge) {
+          for (int j = 1; j < 4; ++j)
+            if (my_nc > 16 * j) tmem_ld16(tSmine + 16 * j, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * j]));
+          if (TRACE && tid == 0) stamp(P.trace, T, 12);
+
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+          uint32_t pmax0 = 0u, pmax1 = 0u;
+          bool exact = t == 0;                           // first tile of the item: the maximum must come first
+          if (!exact) {
+            // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
+            // tile's own maximum is computed on the side (any reference gives the same softmax; the
+            // reference only has to keep P in range).  If the tile turns out to exceed the reference by more
+            // than 2^8, the exact pass below redoes it.
+            const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (my_nc > 16 * j) {
+            for (int j = 0; j < 4; ++j) {
+              if (my_nc > 16 * j) {
+                if (j == 1) tmem_wait_ld();
+                if (edge) {
 #pragma unroll
-                    for (int i = 16 * j; i < 16 * j + 16; ++i)
-                      if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
-                    uint32_t pk[8];
-                    exp16<BF16, 0>(&r[16 * j], pk, scale_log2, neg_m0, sum);
-                    tmem_st8(tPmine + 8 * j, pk);
-                    pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
-                    pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
-                    pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
-                    pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
-                  }
+                  for (int i = 16 * j; i < 16 * j + 16; ++i)
+                    if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
                 }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (my_nc > 16 * j) {
-                    uint32_t pk[8];
-                    exp16<BF16, HBSA_POLY_PAIRS>(&r[16 * j], pk, scale_log2, neg_m0, sum);
-                    tmem_st8(tPmine + 8 * j, pk);
-                    // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
-                    pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
-                    pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
-                    pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
-                    pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
-                  }
-                }
+                uint32_t pk[8];
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                tmem_st8(tSmine + 8 * j, pk);
+                // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
+                pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
+                pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
+                pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
+                pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
               }
-              tr.put(0x22);
-              // A P above 2^8 means the columns exceed the reference by more than the threshold; the row maximum
-              // itself is only computed on that (rare) path.  Rows without a reference yet take it as well.
-              const uint32_t pm = __vimax3_u16x2(pmax0, pmax1, 0u);
-              const uint32_t p_hi = max(pm >> 16, pm & 0xffffu);
-              bool need = p_hi > (BF16 ? 0x4380u : 0x5c00u) || m_ref == -INFINITY;
-              if (__any_sync(0xffffffffu, need)) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (my_nc > 16 * j) max16(&r[16 * j], mx4);
-                const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
-                need = mx_s > m_ref + kRescaleThreshold;
-                if (__any_sync(0xffffffffu, need)) {       // (a row without reference whose columns are all masked needs nothing)
-                  // O and l move to the new reference maximum; needs the previous P V group of the lane
-                  const int hp = h == 1 ? 0 : n_half - 1, Tp = h == 1 ? T : T - 1;
-                  ok = warp_wait(pv_bar(bar_pv_done, L, hp, Tp), pv_par(Tp), abort_flag, budget);
-                  if (!ok) break;
-                  tc_fence_after();
-                  const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
-#pragma unroll 1
-                  for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tOmine + c0, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tOmine + c0, o);
-                  }
-                  tmem_wait_st();
-                  l *= alpha;
-                  if (need) m_ref = mx_s;
-                  exact = true;                            // P of these columns is recomputed against the new reference
-                  sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
-                }
-              }
-            } else {
-              if (edge) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                  if (i > col_limit) r[i] = 0xff800000u;
-              }
+            }
+            if (my_nc <= 16) tmem_wait_ld();
+            // A P above 2^8 means the tile exceeds the reference by more than the threshold; the row maximum
+            // itself is only computed on that (rare) path.  Rows without a reference yet take it as well.
+            const uint32_t pm = __vimax3_u16x2(pmax0, pmax1, 0u);
+            const uint32_t p_hi = max(pm >> 16, pm & 0xffffu);
+            bool need = p_hi > (BF16 ? 0x4380u : 0x5c00u) || m_ref == -INFINITY;
+            if (TRACE && tid == 0) stamp(P.trace, T, 7);
+            if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
                 if (my_nc > 16 * j) max16(&r[16 * j], mx4);
-              m_ref = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            }
-            if (exact) {
-              // ---- P = exp2(S * scale - m) packed to 16 bit, row sum
-              const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+              const float mx_s = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 keeps the order
+              need = mx_s > m_ref + kRescaleThreshold;
+              if (__any_sync(0xffffffffu, need)) {       // (a row without reference whose tile is all masked needs nothing)
+                // O and l move to the new reference maximum; needs the P V product of the previous tile
+                ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
+                if (!ok) break;
+                tc_fence_after();
+                const float alpha = need ? ex2_approx(m_ref - mx_s) : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                  uint32_t o[32];
+                  tmem_ld32(tOmine + c0, o);
+                  tmem_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (my_nc > 16 * j) {
-                  uint32_t pk[8];
-                  exp16<BF16, 0>(&r[16 * j], pk, scale_log2, neg_m, sum);
-                  tmem_st8(tPmine + 8 * j, pk);
+                  for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                  tmem_st32(tOmine + c0, o);
                 }
+                tmem_wait_st();
+                l *= alpha;
+                if (need) m_ref = mx_s;
+                exact = true;                            // P of this tile is recomputed against the new reference
+                sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
               }
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            tr.put(0x23);
-            tmem_wait_st();
-            tr.put(0x24);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p_full + 16u * L + 8u * (uint32_t)h);   // one arrival per warp
-            tr.put(0x30 + h);
+          } else {
+            tmem_wait_ld();
+            if (edge) {
+#pragma unroll
+              for (int i = 0; i < 64; ++i)
+                if (i > col_limit) r[i] = 0xff800000u;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (my_nc > 16 * j) max16(&r[16 * j], mx4);
+            m_ref = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            if (TRACE && tid == 0) stamp(P.trace, T, 7);
           }
+          if (exact) {
+            // ---- P = exp2(S * scale - m) packed to 16 bit over the first half of the S columns, row sum
+            const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (my_nc > 16 * j) {
+                uint32_t pk[8];
+                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m, sum);
+                tmem_st8(tSmine + 8 * j, pk);
+              }
+            }
+          }
+          l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          tmem_wait_st();
+          tc_fence_before();
+          if (TRACE && tid == 0) stamp(P.trace, T, 8);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
+          if (TRACE && tid == 0) stamp(P.trace, T, 9);
         }
         if (!ok) break;
 
         // ---- epilogue: O / l -> global; rows past the q-block end are dropped, rows that saw no key are zeros
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 13);
         const bool live = l > 0.f;
         const float inv = live ? 1.f / l : 0.f;
         const uint64_t inv2 = pack_f32x2(inv, inv);
-        const bool store_row = r_tok < q_end;
-        if (P.lse != nullptr && store_row) {
+        if (P.lse != nullptr) {
           // ln sum exp of the row's scaled scores = ln 2 * (reference + log2 l), whatever reference was used
-          P.lse[(long long)r_tok * p.nhead_q + r_head] = live ? 0.6931471805599453f * (m_ref + log2f(l)) : -INFINITY;
+          const int r_tok = tile_tok0 + (tid >> P.gp_shift);
+          if (r_tok < q_end)
+            P.lse[(long long)r_tok * p.nhead_q + head0 + (tid & (P.gp - 1))] = live ? 0.6931471805599453f * (m_ref + log2f(l)) : -INFINITY;
         }
-        tr.put(0x40);
-        ok = warp_wait(pv_bar(bar_pv_done, L, n_half - 1, T - 1), pv_par(T - 1), abort_flag, budget);
+        ok = warp_wait(bar_of(bar_pv_done, T - 1), par_of(T - 1), abort_flag, budget);
         if (!ok) break;
         tc_fence_after();
-        tr.put(0x50);
-        OutT* const orow = o_base + r_tok * P.o_s0 + r_head * P.o_s1;
-        // 64 columns of O per TMEM round trip (128 would not fit the registers of a thread beside the packing)
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 22);
 #pragma unroll
-        for (int cb = 0; cb < D; cb += 64) {
-          uint32_t oa[64];
-          tmem_ld32(tOmine + cb, *reinterpret_cast<uint32_t(*)[32]>(&oa[0]));
-          tmem_ld32(tOmine + cb + 32, *reinterpret_cast<uint32_t(*)[32]>(&oa[32]));
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t oa[32];
+          tmem_ld32(tOmine + c0, oa);
           tmem_wait_ld();
-          if (cb + 64 >= D) {
-            tc_fence_before();                                             // O is in registers: the lane's next item may overwrite it
+          if (c0 + 32 >= D) {
+            tc_fence_before();                                             // O is in registers: the next item may overwrite it
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_o_free + 8u * L);
+            if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
+            if (TRACE && tid == 0) stamp(P.trace, T - 1, 23);
           }
+          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
+          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
+          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
+          uint4* const st = &ctl->stage[warp][0][0];
 #pragma unroll
-          for (int c0 = 0; c0 < 64; c0 += 32) {
-            uint32_t w[16];
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
+            for (int j = 0; j < 4; ++j) {
+              const int e = i * 8 + j * 2;
               float y0, y1;
-              unpack_f32x2(mul_f32x2(pack_b32x2(oa[c0 + e], oa[c0 + e + 1]), inv2), y0, y1);
-              w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
+              unpack_f32x2(mul_f32x2(pack_b32x2(oa[e], oa[e + 1]), inv2), y0, y1);
+              w[j] = live ? pack2<BF16>(y0, y1) : 0u;
             }
-            if (store_row) {
-              // this thread's 64 bytes of the row: two 256-bit stores when the rows are 32-byte aligned
-              if (P.o_vec32) {
-                st_global_v8(orow + cb + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
-                st_global_v8(orow + cb + c0 + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
-              } else {
+            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  *reinterpret_cast<uint4*>(orow + cb + c0 + 8 * i) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-              }
+          for (int i = 0; i < 4; ++i) {
+            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
+            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
+            const int rg = warp * 32 + rr;                                  // row of the M tile
+            const int tok = tile_tok0 + (rg >> P.gp_shift);
+            if (tok < q_end) {
+              OutT* dst = o_base + tok * P.o_s0 + (head0 + (rg & (P.gp - 1))) * P.o_s1 + c0 + cc * 8;
+              *reinterpret_cast<uint4*>(dst) = val;
             }
           }
+          __syncwarp();
         }
-        tr.put(0x60);
+        if (TRACE && tid == 0) stamp(P.trace, T - 1, 11);
+        ++Iq;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar2(bar_item_done + 16u * L, I));
+      if (lane == 0) mbar_arrive(bar_of(bar_item_done, I));
       ++I;
     }
-    tr.done();
   }
 
   // ---- teardown: every thread gets here (all waits are bounded)
@@ -975,6 +789,10 @@ bool encode_map(EncodeTiledFn fn, CUtensorMap* map, bool bf16, const void* base,
   return r == CUDA_SUCCESS;
 }
 
+long long* g_trace = nullptr;
+long long g_wait_budget = 4000000000ll;   // clock64 ticks a wait inside the kernel may take (about two seconds)
+int g_debug_stall = 0;
+
 int sm_count() {
   static int cached[64] = {};
   int dev = 0;
@@ -987,19 +805,14 @@ int sm_count() {
   return cached[dev];
 }
 
-long long* g_trace = nullptr;
-long long g_wait_budget = 4000000000ll;   // clock64 ticks a wait inside the kernel may take (about two seconds)
-int g_debug_stall = 0;
-
 }  // namespace
 
 void sm100_set_wait_budget(long long clocks, int stall_producer) {
   g_wait_budget = clocks > 0 ? clocks : 4000000000ll;
   g_debug_stall = stall_producer ? 1 : 0;
 }
-
 void sm100_set_trace(long long* device_buffer) { g_trace = device_buffer; }
-size_t sm100_trace_bytes() { return (size_t)kTraceRegions * kTraceCap * sizeof(long long); }
+size_t sm100_trace_bytes() { return ((size_t)kTraceTiles * kTraceSlots + 2 * kTraceCtas) * sizeof(long long); }
 
 int sm100_kv_tile_rows(int kbs) {
   if (kbs <= kTileRowsMax) return kbs;
@@ -1053,24 +866,11 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.wait_budget = g_wait_budget;
   P.debug_stall = g_debug_stall;
   P.trace = g_trace;
-  P.o_vec32 = ((uintptr_t)a.o % 32 == 0 && (a.o_stride[0] * 2) % 32 == 0 && (a.o_stride[1] * 2) % 32 == 0) ? 1 : 0;
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
   if (P.total_items <= 0) { *err_text = "no work items"; return HBSA_ERR_SHAPE; }
-  const long long pairs = (P.total_items + 1) / 2;               // two items in flight per persistent CTA
-  const long long resident = sm_count();
-  const unsigned grid = (unsigned)(pairs < resident ? pairs : resident);
-
-  // shared memory: two Q tiles, the K/V ring, the control block, and up to 1023 bytes of alignment slack
-  const size_t q_bytes = 2u * 128u * (size_t)p.headdim * 2u;
-  P.slot_bytes = (uint32_t)P.nt * (uint32_t)p.headdim * 2u;       // a multiple of 1024 for every legal (nt, headdim)
-  const size_t fixed = q_bytes + sizeof(Control) + 1024u;
-  long long n_slots = ((long long)kSmemLimit - (long long)fixed) / (long long)P.slot_bytes;
-  if (n_slots > kMaxSlots) n_slots = kMaxSlots;
-  if (n_slots < kMinSlots) { *err_text = "shared memory cannot hold the K/V ring"; return HBSA_ERR_UNSUPPORTED; }
-  P.n_slots = (int)n_slots;
-  size_t smem = fixed + (size_t)P.n_slots * P.slot_bytes;
-  if (smem < kSmemLimit / 2 + 1024) smem = kSmemLimit / 2 + 1024;  // one CTA per SM: each one takes all 512 TMEM columns
+  const long long resident = 2ll * sm_count();                  // two persistent CTAs per SM
+  const unsigned grid = (unsigned)(P.total_items < resident ? P.total_items : resident);
 
   CUtensorMap tq, tk, tv;
   if (!encode_map(fn, &tq, bf16, a.q, p.headdim, p.nhead_q, a.total_q, a.q_stride[0], a.q_stride[1], gp, P.tt) ||
@@ -1080,6 +880,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     return HBSA_ERR_UNSUPPORTED;
   }
 
+  const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
 #define HBSA_LAUNCH_SM100(D_, BF_, TR_)                                                                   \
   do {                                                                                                   \

@@ -71,6 +71,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// Same, but looks at the clock only: for the last wait of a thread that has already given up and only wants
+// its own asynchronous work to finish before the CTA tears down.
+__device__ __forceinline__ bool mbar_wait_clock(uint32_t bar, uint32_t parity, long long budget) {
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > budget) return false;
+  }
+}
+
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -245,8 +245,10 @@ def HBSAttention_csr(q, k, v, cu_q_seqlens, cu_k_seqlens, csr_row_ptr, csr_col_i
 
 
 def block_decisions_csr(q, k, cu_q_seqlens, cu_k_seqlens, csr_row_ptr, csr_col_idx, num_q_block, num_k_block,
-                        q_block_size, k_block_size, causal):
-    """``block_decisions`` for a CSR block mask (see ``HBSAttention_csr``)."""
+                        q_block_size, k_block_size, causal, want_bitmap=True):
+    """``block_decisions`` for a CSR block mask (see ``HBSAttention_csr``).  With ``want_bitmap=False`` only the counts
+    are computed and the first element of the result is None (the dense bitmap of a packed long-context problem can be
+    far larger than the problem itself)."""
     cu_q32, cu_k32 = _prepare(q, k, k, cu_q_seqlens, cu_k_seqlens, csr_row_ptr)
     nhk = k.shape[1]
     row_ptr, col_idx = _check_csr(csr_row_ptr, csr_col_idx, nhk, num_q_block)
@@ -256,13 +258,14 @@ def block_decisions_csr(q, k, cu_q_seqlens, cu_k_seqlens, csr_row_ptr, csr_col_i
         ws = alloc_workspace(nhk, num_q_block, num_k_block, cu_q32.numel() - 1, dev)
         args = make_args(q, k, k, None, cu_q32, cu_k32, None, q_block_size, k_block_size, causal, 1.0,
                          num_q_block, num_k_block, ws, _lib.HBSA_IMPL_AUTO, csr=(row_ptr, col_idx))
-        dec = torch.empty((nhk, num_q_block, num_k_block), dtype=torch.uint8, device=dev)
+        dec = torch.empty((nhk, num_q_block, num_k_block), dtype=torch.uint8, device=dev) if want_bitmap else None
         counts = torch.empty((nhk, num_q_block), dtype=torch.int32, device=dev)
-        rc = lib.hbsa_block_decisions(ctypes.byref(args), dec.data_ptr(), counts.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        rc = lib.hbsa_block_decisions(ctypes.byref(args), dec.data_ptr() if want_bitmap else None, counts.data_ptr(),
+                                      torch.cuda.current_stream(dev).cuda_stream)
         if rc != 0:
             raise RuntimeError(f"hbsa_block_decisions failed ({rc}): {_lib.last_error()}")
         _state["last_workspace"] = ws
-    return dec.bool(), counts
+    return (dec.bool() if want_bitmap else None), counts
 
 
 class MaskSchedule:

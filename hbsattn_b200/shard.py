@@ -51,6 +51,31 @@ def unit_flops(decisions, cu_q_seqlens, cu_k_seqlens, q_block_size: int, k_block
     return out
 
 
+def active_plane(mask_plane: torch.Tensor, q_len: int, k_len: int, q_block_size: int, k_block_size: int, causal: bool) -> torch.Tensor:
+    """Valid/skip decision of one unit from its own mask plane ``[nqb, nkb]`` (bool, any device): the pair (qb, kb) is
+    computed iff the mask has it and - under a causal mask aligned bottom-right - the first key of kb is not beyond
+    what the last row of qb may see: ``kb * k_block_size <= min((qb + 1) * q_block_size, q_len) - 1 + (k_len - q_len)``.
+    This is the block-level consequence of the element mask of ``hbsattn/reference.py:56-89``, the same rule the
+    schedule kernel applies on the device."""
+    if not causal:
+        return mask_plane.clone()
+    nqb, nkb = mask_plane.shape
+    dev = mask_plane.device
+    last_row = torch.clamp((torch.arange(nqb, device=dev) + 1) * q_block_size, max=q_len) - 1
+    limit = last_row + (k_len - q_len)
+    first_key = torch.arange(nkb, device=dev) * k_block_size
+    return mask_plane & (first_key[None, :] <= limit[:, None])
+
+
+def plane_flops(active: torch.Tensor, q_len: int, k_len: int, q_block_size: int, k_block_size: int, headdim: int, group: int) -> float:
+    """FLOPs over the active pairs of one unit plane (``4 * rows(qb) * rows(kb) * headdim`` per pair and q-head)."""
+    nqb, nkb = active.shape
+    dev = active.device
+    rq = torch.clamp(q_len - torch.arange(nqb, device=dev) * q_block_size, max=q_block_size).to(torch.float64)
+    rk = torch.clamp(k_len - torch.arange(nkb, device=dev) * k_block_size, max=k_block_size).to(torch.float64)
+    return float((active.to(torch.float64) * rq[:, None] * rk[None, :]).sum().item()) * 4.0 * headdim * group
+
+
 def plan_units(flops: np.ndarray, world_size: int) -> List[List[Unit]]:
     """Longest-processing-time-first assignment of the ``[batch, nhead_k]`` units to ``world_size`` ranks.
 

@@ -161,8 +161,9 @@ int hbsa_attention(const hbsa_forward_args* args, void* stream);
 /*
  * The per-block valid/skip decision the forward uses, for checking and FLOP accounting.
  * Same arguments as hbsa_forward (q,k,v,o may be NULL).  Writes
- *   decisions  uint8[nhead_k * num_q_block * num_k_block]  1 = the block pair is computed
- *   counts     int32[nhead_k * num_q_block] or NULL         active k-blocks per (kv-head, q-block)
+ *   decisions  uint8[nhead_k * num_q_block * num_k_block] or NULL   1 = the block pair is computed
+ *   counts     int32[nhead_k * num_q_block] or NULL                  active k-blocks per (kv-head, q-block)
+ * (at least one of the two; the bitmap of a long-context problem can be far larger than its inputs)
  * The rule is the block-level consequence of the element mask of hbsattn/reference.py:56-89.
  */
 int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int32_t* counts,
@@ -185,11 +186,10 @@ int hbsa_read_status(const void* workspace, int32_t* status_out, void* stream);
  * Applies to launches made after the call. */
 void hbsa_debug_set_wait_budget(long long clocks, int stall_producer);
 
-/* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes() bytes is
- * set, four threads of the first CTA of every tensor-core attention launch (the MMA thread, one thread of each
- * lane's softmax warps, one thread of the loader warp) write clock64() stamps of their pipeline events into
- * it: four regions of 8192 int64, entry 0 of a region = number of stamps, every other entry = clock << 8 | event
- * code.  NULL switches it off (the default); the kernel that runs then contains no stamp code. */
+/* Debugging aid (process-wide, not thread-safe): while a device buffer of hbsa_debug_trace_bytes()
+ * bytes is set, the first CTA of every tensor-core attention launch writes clock64() stamps of its
+ * pipeline events into it (96 tiles x 32 int64 slots, then start time and SM of the first 512 CTAs).
+ * NULL switches it off (the default); the kernel that runs then contains no stamp code. */
 size_t hbsa_debug_trace_bytes(void);
 void hbsa_debug_set_trace(void* device_buffer);
 

@@ -1,4 +1,4 @@
-"""Parity at the benchmark's own sizes (BASELINE configurations 2, 3 and 5; 4 in a 16k-token cut).
+"""Parity at the benchmark's own sizes (BASELINE configurations 2, 3, 4 and 5, and a 16k-token cut of 4).
 
 The whole output is compared with the generic CUDA-core kernel (a second, independently written
 implementation), and randomly chosen (sample, kv-head) units - which are independent of each other,
@@ -28,10 +28,13 @@ def _forward(hb, wl, family):
         hb.set_kernel_family("auto")
 
 
-@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg5", "cfg4_16k"])
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg5", "cfg4_16k", "cfg4"])
 def test_benchmark_workload_parity(name):
     import hbsattn_b200 as hb
     dev = torch.device("cuda", torch.cuda.current_device())
+    if name == "cfg4" and torch.cuda.get_device_properties(dev).total_memory < 40 * 2 ** 30:
+        pytest.skip("the 65536-token workload holds 17 GB of q/k/v/o plus two outputs")
+    torch.cuda.empty_cache()
     wl = bench.make_workload(name, 0, dev)
     w = wl["w"]
     out = _forward(hb, wl, "sm100")
