@@ -79,6 +79,7 @@ struct Sm100Params {
   int n_head_sub;              // group / gp
   int tt;                      // tokens per M tile = 128 / gp
   int tiles_per_qblock;
+  int o_vec32;                 // output rows are 32-byte aligned: 256-bit stores
   int items_per_row;           // n_head_sub * tiles_per_qblock
   long long total_items;       // rows * items_per_row
   float scale_log2;
@@ -117,7 +118,6 @@ struct __align__(16) Control {
   int abort_flag;
   int tile_k0[4];
   ItemSlot slot[2];
-  uint4 stage[kSoftmaxWarps][32][4];   // per softmax warp: 32 rows x 64 bytes of output on their way to coalesced global stores
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -441,7 +441,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // P V side: the items whose tiles are in flight, per tile "first of its item" / "last of its item"
       int pT = 0;                    // next tile to issue P V for (pT <= qT <= pT + 2)
       int pIq = 0;                   // items with tiles whose first P V has been issued
-      int fl_first[2] = {0, 0}, fl_last[2] = {0, 0}, fl_item[2] = {0, 0};   // indexed by tile & 1
+      // per in-flight tile (tile & 1): packed flags  bit 0 first of its item, bit 1 last of its item, bits 2.. item number
+      int fl0 = 0, fl1 = 0;
       long long t_progress = clock64();
       while (true) {
         bool progress = false;
@@ -462,7 +463,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (pT < qT) {
           bool ready = mbar_test(bar_of(bar_p_full, pT), par_of(pT)) && mbar_test(bar_of(bar_v_full, pT), par_of(pT));
           // the first P V of an item overwrites O: the epilogue of the previous item must have read it
-          if (ready && fl_first[pT & 1] && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
+          const int fl = (pT & 1) ? fl1 : fl0;
+          if (ready && (fl & 1) && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
           if (ready) {
             // No tcgen05.fence::after_thread_sync here in the shipped build: P(t) is complete in TMEM before
             // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip was
@@ -471,12 +473,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tc_fence_after();
 #endif
             if (TRACE) stamp(P.trace, pT, 4);
-            if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, fl_first[pT & 1] != 0);
-            else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, fl_first[pT & 1] != 0);
+            if (pT & 1) issue_pv(ksteps, tO, pa1, vd1, idesc_pv, (fl & 1) != 0);
+            else issue_pv(ksteps, tO, pa0, vd0, idesc_pv, (fl & 1) != 0);
             tc_commit(bar_of(bar_pv_done, pT));
             if (TRACE) stamp(P.trace, pT, 5);
-            if (fl_first[pT & 1]) ++pIq;
-            if (fl_last[pT & 1]) mbar_arrive(bar_of(bar_item_done, fl_item[pT & 1]));   // through with the item
+            if (fl & 1) ++pIq;
+            if (fl & 2) mbar_arrive(bar_of(bar_item_done, fl >> 2));       // through with the item
             ++pT;
             progress = true;
           }
@@ -497,9 +499,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             else issue_qk<D / 16>(tSb, qd, kd0, idesc_qk);
             tc_commit(bar_of(bar_s_full, qT));
             if (TRACE) stamp(P.trace, qT, 3);
-            fl_first[qT & 1] = q_first ? 1 : 0;
-            fl_last[qT & 1] = q_left == 1 ? 1 : 0;
-            fl_item[qT & 1] = qI;
+            const int fl_new = (q_first ? 1 : 0) | (q_left == 1 ? 2 : 0) | (qI << 2);
+            if (qT & 1) fl1 = fl_new; else fl0 = fl_new;
             ++qT;
             if (q_first) ++qIq;
             q_first = false;
@@ -686,46 +687,41 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         if (TRACE && tid == 0) stamp(P.trace, T - 1, 22);
+        // 64 columns of O per TMEM round trip; every thread writes its own row, 32 bytes (one full sector) per store
+        // when the output rows are 32-byte aligned, 16 bytes otherwise
+        const int r_tok_o = tile_tok0 + (tid >> P.gp_shift);
+        const bool store_row = r_tok_o < q_end;
+        OutT* const orow = o_base + r_tok_o * P.o_s0 + (head0 + (tid & (P.gp - 1))) * P.o_s1;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t oa[32];
-          tmem_ld32(tOmine + c0, oa);
+        for (int cb = 0; cb < D; cb += 64) {
+          uint32_t oa[64];
+          tmem_ld32(tOmine + cb, *reinterpret_cast<uint32_t(*)[32]>(&oa[0]));
+          tmem_ld32(tOmine + cb + 32, *reinterpret_cast<uint32_t(*)[32]>(&oa[32]));
           tmem_wait_ld();
-          if (c0 + 32 >= D) {
+          if (cb + 64 >= D) {
             tc_fence_before();                                             // O is in registers: the next item may overwrite it
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
             if (TRACE && tid == 0) stamp(P.trace, T - 1, 23);
           }
-          // 32 output values of this thread's row = 64 bytes, staged in shared memory (16-byte chunk j of
-          // row r sits at chunk j ^ ((r >> 1) & 3): conflict-free both ways) so that the global stores
-          // below write whole 64-byte runs: four lanes per row, eight rows per instruction
-          uint4* const st = &ctl->stage[warp][0][0];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w[4];
+          for (int c0 = 0; c0 < 64; c0 += 16) {
+            uint32_t w[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int e = i * 8 + j * 2;
+            for (int e = 0; e < 16; e += 2) {
               float y0, y1;
-              unpack_f32x2(mul_f32x2(pack_b32x2(oa[e], oa[e + 1]), inv2), y0, y1);
-              w[j] = live ? pack2<BF16>(y0, y1) : 0u;
+              unpack_f32x2(mul_f32x2(pack_b32x2(oa[c0 + e], oa[c0 + e + 1]), inv2), y0, y1);
+              w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
             }
-            st[lane * 4 + (i ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int rr = (lane >> 2) + 8 * i, cc = lane & 3;
-            const uint4 val = st[rr * 4 + (cc ^ ((rr >> 1) & 3))];
-            const int rg = warp * 32 + rr;                                  // row of the M tile
-            const int tok = tile_tok0 + (rg >> P.gp_shift);
-            if (tok < q_end) {
-              OutT* dst = o_base + tok * P.o_s0 + (head0 + (rg & (P.gp - 1))) * P.o_s1 + c0 + cc * 8;
-              *reinterpret_cast<uint4*>(dst) = val;
+            if (store_row) {
+              if (P.o_vec32) {
+                st_global_v8(orow + cb + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+              } else {
+                *reinterpret_cast<uint4*>(orow + cb + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(orow + cb + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+              }
             }
           }
-          __syncwarp();
         }
         if (TRACE && tid == 0) stamp(P.trace, T - 1, 11);
         ++Iq;
@@ -864,6 +860,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   P.items_per_row = P.n_head_sub * P.tiles_per_qblock;
   P.scale_log2 = p.scale * 1.4426950408889634f;
   P.wait_budget = g_wait_budget;
+  P.o_vec32 = ((uintptr_t)a.o % 32 == 0 && (a.o_stride[0] * 2) % 32 == 0 && (a.o_stride[1] * 2) % 32 == 0) ? 1 : 0;
   P.debug_stall = g_debug_stall;
   P.trace = g_trace;
 

@@ -87,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait_clock(uint32_t bar, uint32_t parity, l
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 3-D tiled load global -> shared (this CTA), completion on an mbarrier of this CTA. No multicast.
+// 3-D tiled load global -> shared (this CTA), completion on an mbarrier of this CTA; one destination CTA only.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
