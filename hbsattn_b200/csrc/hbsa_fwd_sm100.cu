@@ -202,7 +202,9 @@ __device__ __forceinline__ void issue_pv(int n, uint32_t tO, const uint32_t (&pa
 
 // TRACE = true is the instantiation that runs while a debug trace buffer is set; the shipped path carries
 // no stamp code at all.
-template <int D, bool BF16, bool TRACE>
+// NT > 0 fixes the rows of a K/V tile at compile time (the common 64-row case then has no branches on the tile
+// width); NT = 0 reads them from the parameters.
+template <int D, bool BF16, bool TRACE, int NT>
 __global__ void __launch_bounds__(kThreads, 2)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100Params P) {
@@ -277,8 +279,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   const long long budget = P.wait_budget;
-  const uint32_t kv_tile_bytes = (uint32_t)P.nt * D * 2u;
-  const uint32_t kv_panel_bytes = (uint32_t)P.nt * 128u;
+  const int nt = NT > 0 ? NT : P.nt;
+  const uint32_t kv_tile_bytes = (uint32_t)nt * D * 2u;
+  const uint32_t kv_panel_bytes = (uint32_t)nt * 128u;
 
   if (warp == kProducerWarp) {
     // =============================== work fetch + TMA producer ===============================
@@ -367,7 +370,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const int jj = csr ? __shfl_sync(0xffffffffu, val_cur, pos) : base + pos;
           const int blk_k0 = jj * p.kbs;
           for (int sub = 0; sub < P.n_sub && ok; ++sub) {
-            const int k0 = blk_k0 + sub * P.nt;
+            const int k0 = blk_k0 + sub * nt;
             if (k0 >= rec.k_len) break;
             if (T >= 2) ok = warp_wait(bar_of(bar_s_full, T), par_of(T - 2), abort_flag, budget);
             if (!ok) break;
@@ -410,9 +413,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // S(t+2) writes.  The thread polls with non-blocking probes and issues whichever of "next P V" / "next
     // S" has its inputs ready; a clock budget bounds the loop.
     if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc(BF16, false, false, 128, P.nt);
+      const uint32_t idesc_qk = make_idesc(BF16, false, false, 128, nt);
       const uint32_t idesc_pv = make_idesc(BF16, false, true, 128, D);
-      const int ksteps = P.nt >> 4;
+      const int ksteps = nt >> 4;
       const uint32_t desc_hi = smem_desc_hi(1024u);
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
       // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
@@ -529,7 +532,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // =============================== softmax + epilogue ===============================
     const int row = tid;                             // 0..127: row of the M tile = TMEM lane
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    const int my_nc = P.nt;                          // columns of a tile: 16, 32, 48 or 64
+    const int my_nc = nt;                            // columns of a tile: 16, 32, 48 or 64
     const uint32_t tOmine = tmem_base + kTmemOCol + lane_off;
     const float scale_log2 = P.scale_log2;
     int I = 0, Iq = 0, T = 0;
@@ -879,15 +882,20 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
 
   const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
-#define HBSA_LAUNCH_SM100(D_, BF_, TR_)                                                                   \
+#define HBSA_LAUNCH_SM100(D_, BF_, TR_, NT_)                                                              \
   do {                                                                                                   \
-    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, TR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    e = cudaFuncSetAttribute(fwd_sm100_kernel<D_, BF_, TR_, NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess) {                                                                              \
-      fwd_sm100_kernel<D_, BF_, TR_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);                   \
+      fwd_sm100_kernel<D_, BF_, TR_, NT_><<<grid, kThreads, smem, stream>>>(tq, tk, tv, P);              \
       e = cudaGetLastError();                                                                            \
     }                                                                                                    \
   } while (0)
-#define HBSA_LAUNCH_SM100_T(D_, BF_) do { if (P.trace != nullptr) HBSA_LAUNCH_SM100(D_, BF_, true); else HBSA_LAUNCH_SM100(D_, BF_, false); } while (0)
+#define HBSA_LAUNCH_SM100_T(D_, BF_)                                                                      \
+  do {                                                                                                   \
+    if (P.trace != nullptr) HBSA_LAUNCH_SM100(D_, BF_, true, 0);                                         \
+    else if (P.nt == 64) HBSA_LAUNCH_SM100(D_, BF_, false, 64);                                          \
+    else HBSA_LAUNCH_SM100(D_, BF_, false, 0);                                                           \
+  } while (0)
   if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
   else { if (bf16) HBSA_LAUNCH_SM100_T(64, true); else HBSA_LAUNCH_SM100_T(64, false); }
 #undef HBSA_LAUNCH_SM100_T
