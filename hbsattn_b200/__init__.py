@@ -10,13 +10,13 @@ from . import _lib as _lib_module
 
 _lib_module.load()          # fail loudly at import time when the CUDA library is missing
 
-from .hbsa_interface import (HBSAttention, HBSAttention_csr, HBSAttention_with_lse, MaskSchedule, attention_with_schedule,  # noqa: E402
+from .hbsa_interface import (HBSAttention, HBSAttention_csr, attention_backward, HBSAttention_with_lse, MaskSchedule, attention_with_schedule,  # noqa: E402
                              block_decisions, block_decisions_csr, build_schedule, last_status, set_kernel_family)
 from .utils import calculate_blocks  # noqa: E402
 from .host_staged import HostStagedAttention  # noqa: E402
 
 __all__ = ["HBSAttention", "calculate_blocks", "block_decisions", "last_status", "set_kernel_family",
-           "HBSAttention_with_lse", "HBSAttention_csr", "block_decisions_csr", "HostStagedAttention", "MaskSchedule", "build_schedule", "attention_with_schedule", "install_as_hbsattn"]
+           "HBSAttention_with_lse", "HBSAttention_csr", "block_decisions_csr", "attention_backward", "HostStagedAttention", "MaskSchedule", "build_schedule", "attention_with_schedule", "install_as_hbsattn"]
 
 
 def install_as_hbsattn(reference_package_dir=None) -> None:

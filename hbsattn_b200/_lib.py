@@ -28,6 +28,8 @@ EXPORTED_SYMBOLS = (
     "hbsa_attention",
     "hbsa_block_decisions",
     "hbsa_select_impl",
+    "hbsa_backward",
+    "hbsa_backward_workspace_bytes",
     "hbsa_read_status",
     "hbsa_forward_static_scratch",
     "hbsa_static_scratch_status",
@@ -79,6 +81,22 @@ class ForwardArgs(ctypes.Structure):
     ]
 
 
+class BackwardArgs(ctypes.Structure):
+    """Mirror of ``struct hbsa_backward_args``."""
+
+    _fields_ = [
+        ("struct_bytes", ctypes.c_size_t),
+        ("fwd", ForwardArgs),
+        ("d_o", ctypes.c_void_p),
+        ("do_stride", ctypes.c_int64 * 3),
+        ("dq", ctypes.c_void_p),
+        ("dk", ctypes.c_void_p),
+        ("dv", ctypes.c_void_p),
+        ("grad_workspace", ctypes.c_void_p),
+        ("grad_workspace_bytes", ctypes.c_size_t),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -111,6 +129,10 @@ def load() -> ctypes.CDLL:
             getattr(lib, name).argtypes = [ctypes.POINTER(ForwardArgs), vp]
         lib.hbsa_block_decisions.restype = i32
         lib.hbsa_block_decisions.argtypes = [ctypes.POINTER(ForwardArgs), vp, vp, vp]
+        lib.hbsa_backward.restype = i32
+        lib.hbsa_backward.argtypes = [ctypes.POINTER(BackwardArgs), vp]
+        lib.hbsa_backward_workspace_bytes.restype = ctypes.c_size_t
+        lib.hbsa_backward_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64, i32, i32, i32]
         lib.hbsa_select_impl.restype = i32
         lib.hbsa_select_impl.argtypes = [ctypes.POINTER(ForwardArgs)]
         lib.hbsa_read_status.restype = i32
@@ -125,7 +147,7 @@ def load() -> ctypes.CDLL:
         lib.hbsa_debug_set_trace.argtypes = [vp]
         lib.hbsa_debug_set_wait_budget.restype = None
         lib.hbsa_debug_set_wait_budget.argtypes = [ctypes.c_longlong, i32]
-        if lib.hbsa_version() != 3:
+        if lib.hbsa_version() != 4:
             raise ImportError("libhbsattn_b200.so was built from a different ABI version")
         _lib = lib
         return lib

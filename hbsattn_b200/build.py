@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libhbsattn_b200.so")
 STRICT_LIB_PATH = os.path.join(PKG_DIR, "libhbsattn_b200_strict.so")
 SOURCES = ["hbsa_api.cu", "hbsa_schedule.cu", "hbsa_fwd_generic.cu", "hbsa_fwd_sm100.cu",
-           "hbsa_static_scratch.cu"]
+           "hbsa_bwd_generic.cu", "hbsa_static_scratch.cu"]
 HEADERS = ["hbsa_common.cuh", "sm100_ptx.cuh", os.path.join("..", "..", "include", "hbsattn_b200.h")]
 
 

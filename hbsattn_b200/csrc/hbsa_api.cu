@@ -177,6 +177,30 @@ int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int3
   return 0;
 }
 
+size_t hbsa_backward_workspace_bytes(int64_t total_q, int64_t total_k, int nhead_q, int nhead_k, int headdim) {
+  if (total_q < 0 || total_k < 0 || nhead_q <= 0 || nhead_k <= 0 || headdim <= 0) return 0;
+  return hbsa::backward_workspace_bytes(total_q, total_k, nhead_q, nhead_k, headdim);
+}
+
+int hbsa_backward(const hbsa_backward_args* b, void* stream_) {
+  if (!b) return fail(HBSA_ERR_NULL, "args is NULL");
+  if (b->struct_bytes != sizeof(hbsa_backward_args)) return fail(HBSA_ERR_STRUCT, "hbsa_backward_args.struct_bytes does not match this library");
+  hbsa::Problem p;
+  int rc = make_problem(&b->fwd, true, &p);
+  if (rc != 0) return rc;
+  if (!b->d_o || !b->dq || !b->dk || !b->dv || !b->grad_workspace) return fail(HBSA_ERR_NULL, "d_o, dq, dk, dv and grad_workspace must not be NULL");
+  if (!b->fwd.lse) return fail(HBSA_ERR_NULL, "the backward needs the lse of the forward (hbsa_forward_args.lse)");
+  if (b->grad_workspace_bytes < hbsa::backward_workspace_bytes(b->fwd.total_q, b->fwd.total_k, b->fwd.nhead_q, b->fwd.nhead_k, b->fwd.headdim))
+    return fail(HBSA_ERR_WORKSPACE, "grad_workspace is smaller than hbsa_backward_workspace_bytes()");
+  if (((uintptr_t)b->grad_workspace) % 256 != 0) return fail(HBSA_ERR_WORKSPACE, "grad_workspace must be 256-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  hbsa::Workspace ws = hbsa::make_workspace(b->fwd.workspace, p.nhead_k, p.num_q_block, p.num_k_block, p.batch);
+  cudaError_t e = hbsa::launch_schedule(p, ws, nullptr, stream);
+  if (e != cudaSuccess) return fail_cuda(e, "hbsa_backward (schedule)");
+  e = hbsa::launch_backward_generic(p, ws, *b, stream);
+  return e == cudaSuccess ? 0 : fail_cuda(e, "hbsa_backward");
+}
+
 size_t hbsa_debug_trace_bytes(void) { return hbsa::sm100_trace_bytes(); }
 
 void hbsa_debug_set_trace(void* device_buffer) { hbsa::sm100_set_trace(static_cast<long long*>(device_buffer)); }

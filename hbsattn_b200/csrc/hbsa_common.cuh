@@ -142,6 +142,8 @@ void sm100_set_trace(long long* device_buffer);
 size_t sm100_trace_bytes();
 cudaError_t launch_forward_generic(const Problem& p, const Workspace& ws, const hbsa_forward_args& a,
                                    cudaStream_t stream);
+size_t backward_workspace_bytes(long long total_q, long long total_k, int nhead_q, int nhead_k, int headdim);
+cudaError_t launch_backward_generic(const Problem& p, const Workspace& ws, const hbsa_backward_args& b, cudaStream_t stream);
 // Returns nullptr when eligible, else a static string saying why not.
 const char* sm100_ineligible_reason(const hbsa_forward_args& a, float scale);
 // err_text receives a message when a negative HBSA_ERR_* is returned.

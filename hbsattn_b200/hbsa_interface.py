@@ -151,13 +151,19 @@ class _HBSAttentionFunction(torch.autograd.Function):
         cu_q32, cu_k32 = _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask)
         lib = _lib.load()
         dev = q.device
+        want_grad = any(ctx.needs_input_grad[:3])
         with torch.cuda.device(dev):
             out = torch.empty(q.shape, dtype=q.dtype, device=dev)
             if q.shape[0] == 0:
                 return out
             ws = alloc_workspace(k.shape[1], num_q_block, num_k_block, cu_q32.numel() - 1, dev)
+            # the backward starts from the log-sum-exp of every row: keep it when a gradient is wanted
+            lse = torch.empty((q.shape[0], q.shape[1]), dtype=torch.float32, device=dev) if want_grad else None
             args = make_args(q, k, v, out, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, softmax_scale,
-                             num_q_block, num_k_block, ws, _IMPLS[_state["impl"]])
+                             num_q_block, num_k_block, ws, _IMPLS[_state["impl"]], lse=lse)
+            if want_grad:
+                ctx.save_for_backward(q, k, v, out, lse, cu_q32, cu_k32, block_mask)
+                ctx.hbsa = (int(q_block_size), int(k_block_size), bool(causal), softmax_scale, int(num_q_block), int(num_k_block))
             stream = torch.cuda.current_stream(dev).cuda_stream
             rc = lib.hbsa_forward(ctypes.byref(args), stream)
             if rc != 0:
@@ -175,10 +181,54 @@ class _HBSAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        raise NotImplementedError("It does not support gradient propagation yet")
+        """dq, dk, dv over the active block pairs (``hbsa_backward`` of the C ABI).  The reference raises
+        ``NotImplementedError`` here (``hbsattn/hbsa_interface.py:30-32``)."""
+        q, k, v, out, lse, cu_q32, cu_k32, block_mask = ctx.saved_tensors
+        qbs, kbs, causal, softmax_scale, nqb, nkb = ctx.hbsa
+        dq, dk, dv = attention_backward(q, k, v, out, lse, do, cu_q32, cu_k32, block_mask, qbs, kbs, causal, softmax_scale, nqb, nkb)
+        return (dq, dk, dv) + (None,) * 16
 
 
 HBSAttention = _HBSAttentionFunction.apply
+
+
+def attention_backward(q, k, v, out, lse, d_out, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal,
+                       softmax_scale=None, num_q_block=None, num_k_block=None):
+    """Gradients of ``HBSAttention`` with respect to q, k and v, given the forward's output and ``lse``
+    (``HBSAttention_with_lse``): returns ``(dq, dk, dv)`` in the dtype and shapes of q, k, v."""
+    assert lse is not None and lse.dtype == torch.float32 and lse.shape == (q.shape[0], q.shape[1]), "lse must be float32 [total_q, nhead_q]"
+    assert d_out.shape == q.shape, "the output gradient must have the shape of q"
+    cu_q32, cu_k32 = _prepare(q, k, v, cu_q_seqlens, cu_k_seqlens, block_mask)
+    if d_out.dtype != q.dtype:
+        d_out = d_out.to(q.dtype)
+    nqb = block_mask.shape[1] if num_q_block is None else num_q_block
+    nkb = block_mask.shape[2] if num_k_block is None else num_k_block
+    lib = _lib.load()
+    dev = q.device
+    with torch.cuda.device(dev):
+        dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
+        if q.shape[0] == 0 or k.shape[0] == 0:
+            return dq.zero_(), dk.zero_(), dv.zero_()
+        ws = alloc_workspace(k.shape[1], nqb, nkb, cu_q32.numel() - 1, dev)
+        b = _lib.BackwardArgs()
+        b.struct_bytes = ctypes.sizeof(_lib.BackwardArgs)
+        b.fwd = make_args(q, k, v, out, cu_q32, cu_k32, block_mask, q_block_size, k_block_size, causal, softmax_scale, nqb, nkb, ws,
+                          _lib.HBSA_IMPL_AUTO, lse=lse.contiguous())
+        b.d_o = d_out.data_ptr()
+        for i in range(3):
+            b.do_stride[i] = d_out.stride(i)
+        b.dq, b.dk, b.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        nbytes = lib.hbsa_backward_workspace_bytes(q.shape[0], k.shape[0], q.shape[1], k.shape[1], q.shape[2])
+        gws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        b.grad_workspace, b.grad_workspace_bytes = gws.data_ptr(), nbytes
+        rc = lib.hbsa_backward(ctypes.byref(b), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"hbsa_backward failed ({rc}): {_lib.last_error()}")
+        _state["last_workspace"] = ws
+        gws.record_stream(torch.cuda.current_stream(dev))
+    return dq, dk, dv
 
 
 def block_decisions(q, k, cu_q_seqlens, cu_k_seqlens, block_mask, q_block_size, k_block_size, causal):

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define HBSA_ABI_VERSION 3
+#define HBSA_ABI_VERSION 4
 
 /* Element type of q, k, v and o. */
 enum { HBSA_DTYPE_BF16 = 0, HBSA_DTYPE_F16 = 1, HBSA_DTYPE_F32 = 2 };
@@ -168,6 +168,33 @@ int hbsa_attention(const hbsa_forward_args* args, void* stream);
  */
 int hbsa_block_decisions(const hbsa_forward_args* args, uint8_t* decisions, int32_t* counts,
                          void* stream);
+
+/*
+ * Backward of one forward call: dq, dk, dv over the active block pairs.  The reference has none
+ * (hbsattn/hbsa_interface.py:30-32 raises NotImplementedError, README.md:159-163 lists it as future work);
+ * the mathematics is that of hbsattn/reference.py:23-107 differentiated.
+ *
+ *   fwd      the arguments of the forward call: q, k, v, the forward's output in `o`, the forward's `lse`
+ *            (required: run the forward with lse set), mask, sizes, workspace (the schedule is rebuilt in it)
+ *   d_o      gradient of the output, same dtype as q, [total_q, nhead_q, headdim] with element strides do_stride
+ *   dq, dk, dv   results in the dtype of q, contiguous [total_q, nhead_q, headdim] / [total_k, nhead_k, headdim]
+ *   grad_workspace   >= hbsa_backward_workspace_bytes(...) bytes of device memory (fp32 accumulators), 256-byte aligned
+ * CUDA-core kernels for every dtype and headdim <= 256; rows that saw no key get zero gradients.
+ */
+typedef struct hbsa_backward_args {
+  size_t struct_bytes;            /* sizeof(hbsa_backward_args) of the caller */
+  hbsa_forward_args fwd;
+  const void* d_o;
+  int64_t do_stride[3];
+  void* dq;
+  void* dk;
+  void* dv;
+  void* grad_workspace;
+  size_t grad_workspace_bytes;
+} hbsa_backward_args;
+
+size_t hbsa_backward_workspace_bytes(int64_t total_q, int64_t total_k, int nhead_q, int nhead_k, int headdim);
+int hbsa_backward(const hbsa_backward_args* args, void* stream);
 
 /* Which kernel family hbsa_forward would run for these arguments: HBSA_IMPL_GENERIC or
  * HBSA_IMPL_SM100 (or a negative argument error). Launches nothing. */

@@ -27,7 +27,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("HBSATTN_REFERENCE", "/root/reference")
+REF = os.environ.get("HBSATTN_REFERENCE")
+if not REF or not os.path.isfile(os.path.join(REF, "hbsattn", "reference.py")):
+    sys.exit("set HBSATTN_REFERENCE to the checkout of the reference (the directory that holds hbsattn/reference.py)")
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 from hbsattn.reference import hbsattn_reference_v1_base, hbsattn_reference_v3_qkallfirst  # noqa: E402

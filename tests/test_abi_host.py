@@ -32,7 +32,7 @@ def test_header_symbols_are_exported(lib):
     assert declared == set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.hbsa_version() == 3
+    assert lib.hbsa_version() == 4
 
 
 def test_struct_mirror_size(lib):

@@ -241,9 +241,9 @@ def test_api_errors(hb):
         hb.HBSAttention(*args[:6], 24, 16, True, None)
     with pytest.raises(AssertionError):
         hb.HBSAttention(pr["q"][:, :1].repeat(1, 3, 1), *args[1:])
-    q = pr["q"].clone().requires_grad_(True)
+    q = pr["q"].clone().requires_grad_(True)       # the reference raises NotImplementedError here; this package has a backward
     out = hb.HBSAttention(q, *args[1:])
-    with pytest.raises(NotImplementedError):
-        out.float().sum().backward()
+    out.float().sum().backward()
+    assert q.grad is not None and q.grad.shape == q.shape and torch.isfinite(q.grad).all()
     with pytest.raises(RuntimeError):
         hb.HBSAttention(pr["q"].cpu(), *args[1:])
