@@ -247,3 +247,24 @@ def test_api_errors(hb):
     assert q.grad is not None and q.grad.shape == q.shape and torch.isfinite(q.grad).all()
     with pytest.raises(RuntimeError):
         hb.HBSAttention(pr["q"].cpu(), *args[1:])
+
+
+def test_inconsistent_metadata_gives_zeros_and_a_status(hb):
+    """With the calculate_blocks outputs passed in, the call does not synchronise.  If the block counts contradict
+    cu_*_seqlens the device notices: nothing is computed, the output is zeros (not uninitialised memory) and
+    last_status() says so - for both kernel families."""
+    pr = make_problem(9, [256, 300], [256, 300], 4, 2, 128, 128, 128, True, torch.bfloat16, 0.6, "diag")
+    nqb, cqb, qb2b, cnq = hb.calculate_blocks(pr["cu_q"], 128)
+    nkb, ckb, kb2b, cnk = hb.calculate_blocks(pr["cu_k"], 128)
+    wide = torch.zeros(pr["mask"].shape[0], nqb, nkb + 1, dtype=torch.bool, device="cuda")
+    wide[:, :, :nkb] = pr["mask"]
+    for family in ("sm100", "generic"):
+        hb.set_kernel_family(family)
+        try:
+            out = hb.HBSAttention(pr["q"], pr["k"], pr["v"], pr["cu_q"], pr["cu_k"], wide, 128, 128, True, None, "auto",
+                                  nqb, cqb, qb2b, cnq, nkb + 1, ckb, kb2b, cnk)
+            status = hb.last_status()
+        finally:
+            hb.set_kernel_family("auto")
+        assert status[0] == 1 and status[1] == nqb and status[2] == nkb, (family, status[:4])
+        assert (out == 0).all(), family
