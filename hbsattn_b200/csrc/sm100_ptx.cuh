@@ -117,18 +117,7 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// ------------------------------------------------------------------ tcgen05.mma (issued by ONE thread)
-// D[tmem] (+)= A[tmem] * B[smem desc]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
+// ------------------------------------------------------------------ two-wide fp32 arithmetic
 // Two-wide fp32 arithmetic (one instruction, two lanes of a 64-bit register pair).
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
@@ -159,6 +148,7 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   return d;
 }
 
+// ------------------------------------------------------------------ tcgen05.mma (issued by ONE thread)
 // D[tmem] (+)= A[smem desc] * B[smem desc] and D[tmem] (+)= A[tmem] * B[smem desc] with the accumulate flag
 // known at compile time (no predicate set-up from a register in the issue sequence of the single issuing thread).
 template <bool ACCUMULATE>

@@ -268,3 +268,23 @@ def test_inconsistent_metadata_gives_zeros_and_a_status(hb):
             hb.set_kernel_family("auto")
         assert status[0] == 1 and status[1] == nqb and status[2] == nkb, (family, status[:4])
         assert (out == 0).all(), family
+
+
+def test_generic_kernel_takes_any_strides(hb):
+    """q/k/v with a non-unit stride along headdim (a transposed view) and a block mask that is a strided view of a larger
+    tensor: the tensor-core kernel does not take such layouts, the generic kernel must, with the same result as for
+    contiguous copies."""
+    pr = make_problem(12, [150, 90], [200, 70], 4, 2, 64, 32, 48, True, torch.bfloat16, 0.6, "first")
+    q_t = pr["q"].permute(2, 0, 1).contiguous().permute(1, 2, 0)          # same values, headdim stride = total_q * nhead
+    k_t = pr["k"].permute(2, 0, 1).contiguous().permute(1, 2, 0)
+    v_t = pr["v"].permute(1, 0, 2).contiguous().permute(1, 0, 2)          # head-major storage
+    assert q_t.stride(2) != 1 and k_t.stride(2) != 1 and not v_t.is_contiguous()
+    big = torch.zeros(pr["mask"].shape[0], pr["mask"].shape[1] * 2, pr["mask"].shape[2] * 3, dtype=torch.bool, device="cuda")
+    big[:, ::2, ::3] = pr["mask"]
+    mask_v = big[:, ::2, ::3]
+    assert mask_v.stride() != pr["mask"].stride()
+    want = run_forward(hb, pr, None, family="generic")
+    strided = dict(pr, q=q_t, k=k_t, v=v_t, mask=mask_v)
+    got = run_forward(hb, strided, None, family="auto")               # picks the generic kernel by itself
+    assert torch.equal(got, want)
+    check(got, oracle_on(pr))
