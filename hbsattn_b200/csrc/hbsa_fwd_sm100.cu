@@ -21,7 +21,9 @@
 //    One thread issues every MMA; because tcgen05.mma instructions of one thread execute in issue
 //    order, S(t+2) is issued right behind P V(t) into the buffer that P(t) occupies without waiting
 //    for P V(t) to complete (HBSA_STRICT_TCGEN05 builds wait and fence instead; they exist to check this
-//    ordering bit for bit).
+//    ordering bit for bit).  Issuing one tcgen05.mma occupies its thread for 70 to 100 clocks whatever the
+//    shape (measured), so the twelve instructions of a 64-row tile are about half of the tile period: the thread
+//    looks for new inputs between the two products only, and its polling loop is kept to one probe per turn.
 //  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
 //    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
 //    and no shared-memory exchange.  The exponentials of a tile run against the reference maximum of the
@@ -39,7 +41,9 @@
 // of them that have tiles.  Two-entry barrier arrays are indexed by the low bit of the count and
 // complete once per use, so a waiter for count c uses entry c & 1 and parity (c >> 1) & 1:
 //   k_full / v_full [T]: TMA bytes landed          s_full [T]: S = Q K^T done (K stage free again)
-//   p_full [T]: P written (one arrival per warp)   pv_done [T]: O += P V done (V stage free again)
+//   pv_done [T]: O += P V done (V stage free again)
+// P(T) is handed over through a plain shared-memory counter instead (p_count, one increment per softmax warp, never
+// reset): the issuing thread reads it with an ordinary load in its polling loop.
 //   q_full [Iq]: Q tile landed                     o_free [Iq]: epilogue has read O out of TMEM
 //   item_full [I]: item slot written               item_done [I]: all consumers left item I
 #include <cuda.h>
@@ -93,7 +97,7 @@ constexpr int kTraceSlots = 32;      // stamps per tile
 constexpr int kTraceCtas = 512;      // behind the tile stamps: start time (ns) and SM of the first CTAs
 // slots: 0 K issued, 1 V issued, 2 S(t) issue starts, 3 S(t) issued, 4 PV(t) issue starts, 5 PV(t) issued,
 // 6 softmax sees S, 7 row max done, 8 P written, 9 P arrival done, 10 item start, 11 epilogue done,
-// 12 S in registers, 13 epilogue starts, 22 last PV seen complete, 23 O in registers
+// 12 S in registers, 13 epilogue starts, 17 issuer sees P, 18 issuer sees V, 22 last PV seen complete, 23 O in registers
 __device__ __forceinline__ void stamp(long long* trace, int tile, int slot) {
   if (trace != nullptr && blockIdx.x == 0 && tile >= 0 && tile < kTraceTiles) trace[tile * kTraceSlots + slot] = clock64();
 }
@@ -112,10 +116,11 @@ struct ItemSlot {
 
 struct __align__(16) Control {
   unsigned long long item_full[2], item_done[2];
-  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], o_free[2];
+  unsigned long long q_full[2], k_full[2], v_full[2], s_full[2], pv_done[2], o_free[2];
   unsigned long long drain;
   uint32_t tmem_base;
   int abort_flag;
+  unsigned p_count[2];       // arrivals of the softmax warps for the S buffer tile & 1 (never reset: 4 per tile)
   int tile_k0[4];
   ItemSlot slot[2];
 };
@@ -243,7 +248,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t bar_item_full = smem_u32(&ctl->item_full[0]), bar_item_done = smem_u32(&ctl->item_done[0]);
   const uint32_t bar_q_full = smem_u32(&ctl->q_full[0]), bar_k_full = smem_u32(&ctl->k_full[0]);
   const uint32_t bar_v_full = smem_u32(&ctl->v_full[0]), bar_s_full = smem_u32(&ctl->s_full[0]);
-  const uint32_t bar_p_full = smem_u32(&ctl->p_full[0]), bar_pv_done = smem_u32(&ctl->pv_done[0]);
+  const uint32_t bar_pv_done = smem_u32(&ctl->pv_done[0]);
   const uint32_t bar_o_free = smem_u32(&ctl->o_free[0]);
   volatile int* const abort_flag = &ctl->abort_flag;
   volatile int* const tile_k0 = ctl->tile_k0;
@@ -257,12 +262,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(bar_k_full + 8 * i, 1);
       mbar_init(bar_v_full + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_p_full + 8 * i, kSoftmaxWarps);
       mbar_init(bar_pv_done + 8 * i, 1);
       mbar_init(bar_o_free + 8 * i, kSoftmaxWarps);
     }
     mbar_init(smem_u32(&ctl->drain), 1);
     ctl->abort_flag = 0;
+    ctl->p_count[0] = ctl->p_count[1] = 0u;
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -446,7 +451,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       int pIq = 0;                   // items with tiles whose first P V has been issued
       // per in-flight tile (tile & 1): packed flags  bit 0 first of its item, bit 1 last of its item, bits 2.. item number
       int fl0 = 0, fl1 = 0;
-      long long t_progress = clock64();
+      bool v_landed = false, p_seen = false;
+      unsigned idle = 0u;
+      long long t_idle = 0;
       while (true) {
         bool progress = false;
         if (!q_have && !finished && mbar_test(bar_of(bar_item_full, qI), par_of(qI))) {
@@ -464,14 +471,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           progress = true;
         }
         if (pT < qT) {
-          bool ready = mbar_test(bar_of(bar_p_full, pT), par_of(pT)) && mbar_test(bar_of(bar_v_full, pT), par_of(pT));
+          // one probe per idle turn in the steady state: that V(pT) has landed is looked up once and remembered
+          if (!v_landed) {
+            v_landed = mbar_test(bar_of(bar_v_full, pT), par_of(pT));
+            if (TRACE && v_landed) stamp(P.trace, pT, 18);
+          }
+          const bool p_there = *(volatile unsigned*)&ctl->p_count[pT & 1] >= (unsigned)kSoftmaxWarps * ((unsigned)(pT >> 1) + 1u);
+          if (TRACE && !p_seen && p_there) {
+            p_seen = true;
+            stamp(P.trace, pT, 17);
+          }
+          bool ready = v_landed && p_there;
           // the first P V of an item overwrites O: the epilogue of the previous item must have read it
           const int fl = (pT & 1) ? fl1 : fl0;
           if (ready && (fl & 1) && pIq >= 1) ready = mbar_test(bar_of(bar_o_free, pIq - 1), par_of(pIq - 1));
           if (ready) {
             // No tcgen05.fence::after_thread_sync here in the shipped build: P(t) is complete in TMEM before
-            // p_full can flip (tcgen05.wait::st precedes the arrivals), and the MMA is issued after the flip was
-            // observed.  HBSA_STRICT_TCGEN05 builds execute the fence; the two builds must agree bit for bit.
+            // the counter can reach its value (tcgen05.wait::st precedes the increments), and the MMA is issued after
+            // that was observed.  HBSA_STRICT_TCGEN05 builds execute the fence; the two builds must agree bit for bit.
 #ifdef HBSA_STRICT_TCGEN05
             tc_fence_after();
 #endif
@@ -483,6 +500,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (fl & 1) ++pIq;
             if (fl & 2) mbar_arrive(bar_of(bar_item_done, fl >> 2));       // through with the item
             ++pT;
+            v_landed = false;
+            p_seen = false;
             progress = true;
           }
         }
@@ -516,10 +535,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         if (finished && pT == qT) break;
         if (progress) {
-          t_progress = clock64();
-        } else {
+          idle = 0;
+        } else if ((++idle & 63u) == 0u) {                  // give-up checks on one idle turn in 64: they cost as much as a probe
           if (*abort_flag) break;
-          if (clock64() - t_progress > budget) { *abort_flag = 1; break; }
+          const long long now = clock64();
+          if (idle == 64u) t_idle = now;
+          else if (now - t_idle > budget) { *abort_flag = 1; break; }
         }
       }
       // Whatever this thread has issued completes before the CTA gives its tensor memory back, also when it gave up
@@ -670,8 +691,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tc_fence_before();
           if (TRACE && tid == 0) stamp(P.trace, T, 8);
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_of(bar_p_full, T));             // one arrival per warp
-          if (TRACE && tid == 0) stamp(P.trace, T, 9);
+          if (lane == 0) {                                               // one arrival per warp, on a plain shared-memory counter
+            __threadfence_block();
+            atomicAdd(&ctl->p_count[T & 1], 1u);
+          }
+          if (TRACE && lane == 0) stamp(P.trace, T, warp == 0 ? 9 : 13 + warp);        // slots 9, 14, 15, 16: arrival of warps 0..3
         }
         if (!ok) break;
 
