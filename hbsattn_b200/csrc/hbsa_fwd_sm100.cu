@@ -222,7 +222,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   OutT* const o_base = static_cast<OutT*>(P.o);
 
   if (P.ws.status[0] != HBSA_STATUS_OK) {
-    zero_fill_output(o_base, P.o_s0, P.o_s1, 1ll, P.total_q, p.nhead_q, D, P.lse);
+    zero_fill_output(o_base, P.o_s0, P.o_s1, 1ll, P.total_q, p.nhead_q, p.headdim, P.lse);
     return;
   }
   if (TRACE && P.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceCtas) {
@@ -570,7 +570,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (r_tok < q_end) {
           uint4* dst = reinterpret_cast<uint4*>(o_base + r_tok * P.o_s0 + (head0 + (row & (P.gp - 1))) * P.o_s1);
 #pragma unroll
-          for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < D / 8; ++i)
+            if (i * 8 < p.headdim) dst[i] = make_uint4(0, 0, 0, 0);
           if (P.lse != nullptr) P.lse[(long long)r_tok * p.nhead_q + head0 + (row & (P.gp - 1))] = -INFINITY;
         }
       } else {
@@ -740,8 +741,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               unpack_f32x2(mul_f32x2(pack_b32x2(oa[c0 + e], oa[c0 + e + 1]), inv2), y0, y1);
               w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
             }
-            if (store_row) {
-              if (P.o_vec32) {
+            // columns at and past the real head dimension are padding (zeros); it is a multiple of 8
+            if (store_row && cb + c0 < p.headdim) {
+              if (cb + c0 + 8 >= p.headdim) {
+                *reinterpret_cast<uint4*>(orow + cb + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+              } else if (P.o_vec32) {
                 st_global_v8(orow + cb + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
               } else {
                 *reinterpret_cast<uint4*>(orow + cb + c0) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -846,7 +850,7 @@ int sm100_kv_tile_rows(int kbs) {
 
 const char* sm100_ineligible_reason(const hbsa_forward_args& a, float scale) {
   if (a.dtype != HBSA_DTYPE_BF16 && a.dtype != HBSA_DTYPE_F16) return "dtype is not bf16/fp16";
-  if (a.headdim != 64 && a.headdim != 128) return "headdim is not 64 or 128";
+  if (a.headdim % 8 != 0 || a.headdim < 16 || a.headdim > 128) return "headdim is not a multiple of 8 between 16 and 128";
   if (!(scale > 0.f) || !isfinite(scale)) return "softmax_scale is not a positive finite number";
   if (a.q_stride[2] != 1 || a.k_stride[2] != 1 || a.v_stride[2] != 1 || a.o_stride[2] != 1)
     return "headdim stride is not 1";
@@ -904,7 +908,11 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     return HBSA_ERR_UNSUPPORTED;
   }
 
-  const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)p.headdim * 2u + sizeof(Control) + 1024u;
+  // Head dimensions other than 64 and 128 run on the next larger of the two: the TMA boxes reach past the tensors'
+  // innermost extent, the hardware fills those columns of Q, K and V with zeros (so S is exact and the surplus
+  // columns of O are zeros), and the epilogue stores the real columns only.
+  const int d_tile = p.headdim <= 64 ? 64 : 128;
+  const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)d_tile * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
 #define HBSA_LAUNCH_SM100(D_, BF_, TR_, NT_)                                                              \
   do {                                                                                                   \
@@ -920,7 +928,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     else if (P.nt == 64) HBSA_LAUNCH_SM100(D_, BF_, false, 64);                                          \
     else HBSA_LAUNCH_SM100(D_, BF_, false, 0);                                                           \
   } while (0)
-  if (p.headdim == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
+  if (d_tile == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
   else { if (bf16) HBSA_LAUNCH_SM100_T(64, true); else HBSA_LAUNCH_SM100_T(64, false); }
 #undef HBSA_LAUNCH_SM100_T
 #undef HBSA_LAUNCH_SM100

@@ -181,6 +181,45 @@ def test_sm100_parity(hb, case, dtype):
     assert (out.float() - out_g.float()).abs().max().item() <= 2e-2
 
 
+PADDED_D_CASES = [
+    # name, headdim, hq, hk, qbs, kbs, causal: head dimensions the tensor-core kernel pads to 64 / 128 inside its tiles
+    ("d32_mha_32x32", 32, 2, 2, 32, 32, True),
+    ("d32_gqa4_128x128", 32, 8, 2, 128, 128, False),
+    ("d16_mha_64x64", 16, 2, 2, 64, 64, True),
+    ("d40_gqa2_80x48", 40, 4, 2, 80, 48, True),
+    ("d96_mha_128x128", 96, 4, 4, 128, 128, True),
+    ("d96_gqa4_64x256", 96, 8, 2, 64, 256, False),
+    ("d72_mqa_48x80", 72, 4, 1, 48, 80, True),
+    ("d120_gqa2_128x128", 120, 4, 2, 128, 128, False),
+]
+
+
+@pytest.mark.parametrize("case", PADDED_D_CASES, ids=[c[0] for c in PADDED_D_CASES])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_sm100_padded_headdim(hb, case, dtype):
+    """Head dimensions between 16 and 128 that are multiples of 8 run on the tensor-core kernel (the reference pads
+    BLOCK_DIM to a power of two, fwd_triton_auto_tile_size.py:269): oracle parity (a store past the real columns
+    would land in the next head), agreement with the CUDA-core kernel, and - with q given as a view into a wider
+    buffer whose surplus columns hold a poison value - padding that comes from the tensor's extent, not from memory."""
+    name, d, hq, hk, qbs, kbs, causal = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    q_lens = make_lengths(rng, 3, 100, 700)
+    k_lens = make_lengths(rng, 3, 90, 800)
+    pr = make_problem(21, q_lens, k_lens, hq, hk, d, qbs, kbs, causal, dtype, 0.5, "first")
+    out = run_forward(hb, pr, None, family="sm100")
+    gold = oracle_on(pr)
+    check(out, gold)
+    out_g = run_forward(hb, pr, None, family="generic")
+    assert (out.float() - out_g.float()).abs().max().item() <= 2e-2
+    # q as a view with padding columns behind every head: rows stay 16-byte aligned, head dim stride 1
+    wide = torch.full((pr["q"].shape[0], hq, d + 8), 7.0, dtype=dtype, device="cuda")
+    wide[:, :, :d] = pr["q"]
+    sub = dict(pr)
+    sub["q"] = wide[:, :, :d]
+    out_v = run_forward(hb, sub, None, family="sm100")
+    assert torch.equal(out_v, out)
+
+
 def test_sm100_pv_path_only(hb):
     """q = 0 makes every allowed key equally likely, so the output is the mean of the allowed V rows:
     isolates the P (TMEM operand) x V (MN-major shared-memory operand) contraction."""
