@@ -65,7 +65,8 @@ constexpr int kSoftmaxWarps = 4;
 constexpr int kProducerWarp = 4;
 constexpr int kMmaWarp = 5;
 constexpr int kTileRowsMax = 64;      // rows of a K/V tile
-constexpr int kTmemCols = 256;
+// S0, S1 of 64 columns + O of D columns, rounded up to a power of two
+template <int D> struct TmemCols { static constexpr uint32_t value = D > 128 ? 512u : 256u; };
 constexpr uint32_t kSStride = 64u;    // TMEM columns between the two S buffers
 constexpr uint32_t kTmemOCol = 128u;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
@@ -183,7 +184,7 @@ __device__ __forceinline__ uint32_t par_of(int c) { return (uint32_t)(c >> 1) & 
 // The issue sequences of the MMA thread.  Every descriptor and TMEM address is precomputed into
 // registers once per CTA, so a product is nothing but back-to-back tcgen05.mma instructions.
 template <int KSTEPS>
-__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[8], const uint64_t (&kd)[8], uint32_t idesc) {
+__device__ __forceinline__ void issue_qk(uint32_t tS, const uint64_t (&qd)[KSTEPS], const uint64_t (&kd)[KSTEPS], uint32_t idesc) {
   ptx::mma_ss_c<false>(tS, qd[0], kd[0], idesc);
 #pragma unroll
   for (int ks = 1; ks < KSTEPS; ++ks) ptx::mma_ss_c<true>(tS, qd[ks], kd[ks], idesc);
@@ -276,7 +277,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     prefetch_tensormap(&tm_v);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_alloc(smem_u32(&ctl->tmem_base), TmemCols<D>::value);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -425,10 +426,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t kpanel_units = kv_panel_bytes >> 4;
       // Q and K are K-major: 16 head dims further = 32 bytes = 2 descriptor units inside a 64-dim panel.
       // V is MN-major: 16 keys further = 2048 bytes = 128 units.  P: 8 TMEM columns per 16 keys.
-      uint64_t qd[8], kd0[8], kd1[8], vd0[4], vd1[4];
+      uint64_t qd[D / 16], kd0[D / 16], kd1[D / 16], vd0[4], vd1[4];
       uint32_t pa0[4], pa1[4];
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t ko = (uint32_t)(ks >> 2) * kpanel_units + (uint32_t)(ks & 3) * 2u;
         const uint32_t qo = (uint32_t)(ks >> 2) * 1024u + (uint32_t)(ks & 3) * 2u;
         qd[ks] = smem_desc_join(smem_desc_lo(sQ, 16u) + qo, desc_hi);
@@ -768,7 +769,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, TmemCols<D>::value);
   }
   if (tid == 0 && ctl->abort_flag) {
     atomicExch(&P.ws.status[0], HBSA_STATUS_WAIT_LIMIT);
@@ -850,7 +851,7 @@ int sm100_kv_tile_rows(int kbs) {
 
 const char* sm100_ineligible_reason(const hbsa_forward_args& a, float scale) {
   if (a.dtype != HBSA_DTYPE_BF16 && a.dtype != HBSA_DTYPE_F16) return "dtype is not bf16/fp16";
-  if (a.headdim % 8 != 0 || a.headdim < 16 || a.headdim > 128) return "headdim is not a multiple of 8 between 16 and 128";
+  if (a.headdim % 8 != 0 || a.headdim < 16 || a.headdim > 256) return "headdim is not a multiple of 8 between 16 and 256";
   if (!(scale > 0.f) || !isfinite(scale)) return "softmax_scale is not a positive finite number";
   if (a.q_stride[2] != 1 || a.k_stride[2] != 1 || a.v_stride[2] != 1 || a.o_stride[2] != 1)
     return "headdim stride is not 1";
@@ -897,7 +898,9 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
 
   P.total_items = (long long)p.nhead_k * p.num_q_block * P.items_per_row;
   if (P.total_items <= 0) { *err_text = "no work items"; return HBSA_ERR_SHAPE; }
-  const long long resident = 2ll * sm_count();                  // two persistent CTAs per SM
+  // two persistent CTAs per SM; one above 128 head dimensions (O alone takes 256 of the SM's 512 TMEM columns, the
+  // tiles 192 KB of its shared memory)
+  const long long resident = (p.headdim > 128 ? 1ll : 2ll) * sm_count();
   const unsigned grid = (unsigned)(P.total_items < resident ? P.total_items : resident);
 
   CUtensorMap tq, tk, tv;
@@ -911,7 +914,7 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
   // Head dimensions other than 64 and 128 run on the next larger of the two: the TMA boxes reach past the tensors'
   // innermost extent, the hardware fills those columns of Q, K and V with zeros (so S is exact and the surplus
   // columns of O are zeros), and the epilogue stores the real columns only.
-  const int d_tile = p.headdim <= 64 ? 64 : 128;
+  const int d_tile = p.headdim <= 64 ? 64 : p.headdim <= 128 ? 128 : 256;
   const size_t smem = (128u + 4u * (size_t)kTileRowsMax) * (size_t)d_tile * 2u + sizeof(Control) + 1024u;
   cudaError_t e = cudaSuccess;
 #define HBSA_LAUNCH_SM100(D_, BF_, TR_, NT_)                                                              \
@@ -928,7 +931,8 @@ int launch_forward_sm100(const Problem& p, const Workspace& ws, const hbsa_forwa
     else if (P.nt == 64) HBSA_LAUNCH_SM100(D_, BF_, false, 64);                                          \
     else HBSA_LAUNCH_SM100(D_, BF_, false, 0);                                                           \
   } while (0)
-  if (d_tile == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
+  if (d_tile == 256) { if (bf16) HBSA_LAUNCH_SM100_T(256, true); else HBSA_LAUNCH_SM100_T(256, false); }
+  else if (d_tile == 128) { if (bf16) HBSA_LAUNCH_SM100_T(128, true); else HBSA_LAUNCH_SM100_T(128, false); }
   else { if (bf16) HBSA_LAUNCH_SM100_T(64, true); else HBSA_LAUNCH_SM100_T(64, false); }
 #undef HBSA_LAUNCH_SM100_T
 #undef HBSA_LAUNCH_SM100

@@ -27,7 +27,7 @@ extern "C" {
 enum { HBSA_DTYPE_BF16 = 0, HBSA_DTYPE_F16 = 1, HBSA_DTYPE_F32 = 2 };
 
 /* Kernel family. AUTO picks the tcgen05 kernel whenever the problem is eligible
- * (bf16/fp16, headdim a multiple of 8 from 16 to 128, unit stride along headdim, 16-byte aligned rows,
+ * (bf16/fp16, headdim a multiple of 8 from 16 to 256, unit stride along headdim, 16-byte aligned rows,
  * softmax_scale > 0) and the generic CUDA-core kernel otherwise.  Forcing SM100 on an
  * ineligible problem is an argument error.  Both families are CUDA; there is no CPU path. */
 enum { HBSA_IMPL_AUTO = 0, HBSA_IMPL_GENERIC = 1, HBSA_IMPL_SM100 = 2 };

@@ -182,7 +182,7 @@ def test_sm100_parity(hb, case, dtype):
 
 
 PADDED_D_CASES = [
-    # name, headdim, hq, hk, qbs, kbs, causal: head dimensions the tensor-core kernel pads to 64 / 128 inside its tiles
+    # name, headdim, hq, hk, qbs, kbs, causal: head dimensions the tensor-core kernel pads to 64 / 128 / 256 inside its tiles
     ("d32_mha_32x32", 32, 2, 2, 32, 32, True),
     ("d32_gqa4_128x128", 32, 8, 2, 128, 128, False),
     ("d16_mha_64x64", 16, 2, 2, 64, 64, True),
@@ -191,13 +191,18 @@ PADDED_D_CASES = [
     ("d96_gqa4_64x256", 96, 8, 2, 64, 256, False),
     ("d72_mqa_48x80", 72, 4, 1, 48, 80, True),
     ("d120_gqa2_128x128", 120, 4, 2, 128, 128, False),
+    # above 128 the kernel runs one CTA per SM with 512 tensor-memory columns
+    ("d256_mha_128x128", 256, 2, 2, 128, 128, True),
+    ("d256_gqa4_64x80", 256, 4, 1, 64, 80, False),
+    ("d192_gqa2_128x128", 192, 4, 2, 128, 128, True),
+    ("d136_mha_48x64", 136, 2, 2, 48, 64, False),
 ]
 
 
 @pytest.mark.parametrize("case", PADDED_D_CASES, ids=[c[0] for c in PADDED_D_CASES])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
 def test_sm100_padded_headdim(hb, case, dtype):
-    """Head dimensions between 16 and 128 that are multiples of 8 run on the tensor-core kernel (the reference pads
+    """Head dimensions between 16 and 256 that are multiples of 8 run on the tensor-core kernel (the reference pads
     BLOCK_DIM to a power of two, fwd_triton_auto_tile_size.py:269): oracle parity (a store past the real columns
     would land in the next head), agreement with the CUDA-core kernel, and - with q given as a view into a wider
     buffer whose surplus columns hold a poison value - padding that comes from the tensor's extent, not from memory."""

@@ -1,7 +1,7 @@
 """Seeded random problem shapes through both CUDA kernel families, against the fp32 oracle.
 
 Every draw picks batch, ragged q/k lengths (cu_q != cu_k, bottom-right alignment, samples where q is longer than k),
-GQA ratio, head dimension (any multiple of 8 up to 128 for the tensor-core kernel), heterogeneous block sizes (multiples
+GQA ratio, head dimension (any multiple of 8 up to 256 for the tensor-core kernel), heterogeneous block sizes (multiples
 of 16, not only powers of two), causal or not, mask density, dtype and an explicit or default softmax scale - the axes
 of test/test_accuracy.py:17-29 drawn jointly instead of as a grid, at sizes the oracle finishes in well under a second.
 Checked per draw: oracle tolerance (max-abs <= 2e-2 for outputs up to 2 in magnitude, mean-abs <= 1e-3) for both families, agreement of the two
@@ -26,7 +26,7 @@ def draw(seed):
     kbs = int(rng.choice([16, 32, 48, 64, 80, 128, 144, 256]))
     hk = int(rng.choice([1, 2, 3]))
     group = int(rng.choice([1, 2, 3, 4, 8]))
-    d = int(rng.choice([16, 24, 32, 40, 64, 72, 96, 128]))
+    d = int(rng.choice([16, 24, 32, 40, 64, 72, 96, 128, 160, 256]))
     causal = bool(rng.integers(0, 2))
     same = bool(rng.integers(0, 3) == 0)
     q_lens = make_lengths(rng, batch, 1, 700)
