@@ -59,6 +59,13 @@ WORKLOADS = {
                      p=0.3, force="diag", desc="B8 x 16384 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.3 + diagonal"),
     "cfg4": dict(batch=8, q_len=(65536, 65536, 16), k_len="same", hq=32, hk=32, d=128, qbs=128, kbs=128, causal=True,
                  p=0.3, force="diag", desc="B8 x 65536 tokens, Hq32/Hk32, d128, 128x128 blocks, causal, mask p=0.3 + diagonal"),
+    # the cfg2 shape at other head dimensions (the tensor-core kernel pads them to 64 / 128 / 256 inside its tiles)
+    "cfg2_d32": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=32, qbs=128, kbs=128, causal=True,
+                     p=0.1, force="diag", desc="B8 x 8192 tokens, Hq32/Hk32, d32, 128x128 blocks, causal, mask p=0.1 + diagonal"),
+    "cfg2_d96": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=32, hk=32, d=96, qbs=128, kbs=128, causal=True,
+                     p=0.1, force="diag", desc="B8 x 8192 tokens, Hq32/Hk32, d96, 128x128 blocks, causal, mask p=0.1 + diagonal"),
+    "cfg2_d256": dict(batch=8, q_len=(8192, 8192, 16), k_len="same", hq=16, hk=16, d=256, qbs=128, kbs=128, causal=True,
+                      p=0.1, force="diag", desc="B8 x 8192 tokens, Hq16/Hk16, d256, 128x128 blocks, causal, mask p=0.1 + diagonal"),
     "cfg5": dict(batch=16, q_len=(128, 512, 16), k_len=(16384, 32768, 1), hq=64, hk=8, d=64, qbs=16, kbs=128, causal=True,
                  p=0.2, force="diag", desc="B16, q 128-512, k 16384-32768, Hq64/Hk8, d64, 16x128 blocks, bottom-right causal, mask p=0.2 + last valid"),
 }
