@@ -27,9 +27,9 @@
 //  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
 //    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
 //    and no shared-memory exchange.  The exponentials of a tile run against the reference maximum of the
-//    previous tiles while the tile's own maximum is computed alongside; the running output is rescaled in
-//    TMEM (and the tile redone) only when a row maximum grows by more than 2^8.  The arithmetic around the
-//    exponentials is two-wide (fma/add/mul.rn.f32x2).
+//    previous tiles; only when the tile's row sum (which bounds every P of the row) exceeds 2^14 is the row
+//    maximum computed, and the running output rescaled in TMEM (and the tile redone) where it grew by more
+//    than 2^8.  The arithmetic around the exponentials is two-wide (fma/add/mul.rn.f32x2).
 //  * The last CTA to leave rewinds the work cursor, so one schedule serves any number of launches.  With
 //    `lse` set, ln sum exp of every row goes out beside O.
 //
@@ -601,13 +601,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           float sum[4] = {0.f, 0.f, 0.f, 0.f};
-          uint32_t pmax0 = 0u, pmax1 = 0u;
           bool exact = t == 0;                           // first tile of the item: the maximum must come first
           if (!exact) {
-            // Optimistic pass: exponentials against the reference maximum of the previous tiles while the
-            // tile's own maximum is computed on the side (any reference gives the same softmax; the
-            // reference only has to keep P in range).  If the tile turns out to exceed the reference by more
-            // than 2^8, the exact pass below redoes it.
+            // Optimistic pass: exponentials against the reference maximum of the previous tiles (any reference
+            // gives the same softmax; the reference only has to keep P in range).  If the tile turns out to be
+            // out of range, the exact pass below redoes it.
             const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -621,19 +619,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 uint32_t pk[8];
                 exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
                 tmem_st8(tSmine + 8 * j, pk);
-                // P >= 0: 16-bit floats order like unsigned integers, two per word, three words per instruction
-                pmax0 = __vimax3_u16x2(pmax0, pk[0], pk[1]);
-                pmax1 = __vimax3_u16x2(pmax1, pk[2], pk[3]);
-                pmax0 = __vimax3_u16x2(pmax0, pk[4], pk[5]);
-                pmax1 = __vimax3_u16x2(pmax1, pk[6], pk[7]);
               }
             }
             if (my_nc <= 16) tmem_wait_ld();
-            // A P above 2^8 means the tile exceeds the reference by more than the threshold; the row maximum
-            // itself is only computed on that (rare) path.  Rows without a reference yet take it as well.
-            const uint32_t pm = __vimax3_u16x2(pmax0, pmax1, 0u);
-            const uint32_t p_hi = max(pm >> 16, pm & 0xffffu);
-            bool need = p_hi > (BF16 ? 0x4380u : 0x5c00u) || m_ref == -INFINITY;
+            // Whether the reference is stale is read off the tile's row sum, which is there anyway: P >= 0, so no P
+            // exceeds it, and a sum of at most 2^14 keeps every P far inside the range of both 16-bit formats (an
+            // overflowed exponential makes the sum infinite).  The row maximum itself is only computed on that (rare)
+            // path.  Rows without a reference yet take it as well.
+            const float tile_sum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            bool need = !(tile_sum <= 16384.f) || m_ref == -INFINITY;
             if (TRACE && tid == 0) stamp(P.trace, T, 7);
             if (__any_sync(0xffffffffu, need)) {
 #pragma unroll

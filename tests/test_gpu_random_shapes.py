@@ -47,9 +47,10 @@ def test_random_shape(seed):
                       c["p_keep"], c["force"])
     gold = oracle_forward(pr["q"].float(), pr["k"].float(), pr["v"].float(), pr["cu_q_list"], pr["cu_k_list"], pr["mask"],
                           c["qbs"], c["kbs"], c["causal"], c["scale"])
-    # 2e-2 is stated for outputs of order one; a sharp softmax (large explicit scale, few keys) returns single V rows,
-    # and from 4 upwards one bf16 step of the OUTPUT is 0.031 already - the bound grows with the largest output
-    tol = 2e-2 * max(1.0, gold.abs().max().item() / 2.0)
+    # 2e-2 / 1e-3 are stated for outputs of order one; a sharp softmax (large explicit scale, few keys) returns single V
+    # rows, and from 4 upwards one bf16 step of the OUTPUT is 0.031 already - both bounds grow with the largest output
+    grow = max(1.0, gold.abs().max().item() / 2.0)
+    tol, tol_mean = 2e-2 * grow, 1e-3 * grow
     outs = {}
     for family in ("sm100", "generic"):
         hb.set_kernel_family(family)
@@ -61,7 +62,7 @@ def test_random_shape(seed):
             hb.set_kernel_family("auto")
         assert torch.isfinite(out).all(), (family, c)
         st = error_stats(gold, out)
-        assert st["max_abs"] <= tol and st["mean_abs"] <= 1e-3, (family, st, c)
+        assert st["max_abs"] <= tol and st["mean_abs"] <= tol_mean, (family, st, c)
         outs[family] = out
     assert (outs["sm100"].float() - outs["generic"].float()).abs().max().item() <= 2.0 * tol, c
     # rows the oracle leaves without keys are exact zeros in both kernels
