@@ -607,18 +607,33 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // gives the same softmax; the reference only has to keep P in range).  If the tile turns out to be
             // out of range, the exact pass below redoes it.
             const float neg_m0 = m_ref == -INFINITY ? 0.f : -m_ref;
+            // With the tile width fixed at compile time, tiles without masked columns (all but those on the causal
+            // diagonal or at the ragged end of a sample) take a copy of the loop that has no per-group branch; the
+            // test is warp-uniform because the TMEM stores are warp-wide instructions.
+            if (NT > 0 && !__any_sync(0xffffffffu, edge)) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (my_nc > 16 * j) {
-                if (j == 1) tmem_wait_ld();
-                if (edge) {
-#pragma unroll
-                  for (int i = 16 * j; i < 16 * j + 16; ++i)
-                    if (i > col_limit) r[i] = 0xff800000u;                 // -inf: exp2 makes it an exact 0
+              for (int j = 0; j < 4; ++j) {
+                if (my_nc > 16 * j) {
+                  if (j == 1) tmem_wait_ld();
+                  uint32_t pk[8];
+                  exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                  tmem_st8(tSmine + 8 * j, pk);
                 }
-                uint32_t pk[8];
-                exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
-                tmem_st8(tSmine + 8 * j, pk);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (my_nc > 16 * j) {
+                  if (j == 1) tmem_wait_ld();
+                  if (edge) {
+#pragma unroll
+                    for (int i = 16 * j; i < 16 * j + 16; ++i)
+                      if (i > col_limit) r[i] = 0xff800000u;               // -inf: exp2 makes it an exact 0
+                  }
+                  uint32_t pk[8];
+                  exp16<BF16>(&r[16 * j], pk, scale_log2, neg_m0, sum);
+                  tmem_st8(tSmine + 8 * j, pk);
+                }
               }
             }
             if (my_nc <= 16) tmem_wait_ld();
