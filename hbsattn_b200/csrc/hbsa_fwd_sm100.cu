@@ -729,6 +729,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // when the output rows are 32-byte aligned, 16 bytes otherwise
         const int r_tok_o = tile_tok0 + (tid >> P.gp_shift);
         const bool store_row = r_tok_o < q_end;
+        const bool fast_store = store_row && P.o_vec32 != 0 && p.headdim == D;
         OutT* const orow = o_base + r_tok_o * P.o_s0 + (head0 + (tid & (P.gp - 1))) * P.o_s1;
 #pragma unroll
         for (int cb = 0; cb < D; cb += 64) {
@@ -741,6 +742,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(bar_o_free, Iq));
             if (TRACE && tid == 0) stamp(P.trace, T - 1, 23);
+          }
+          if (fast_store) {
+            // the common case (row inside the q-block, 32-byte aligned rows, no padded columns): no branch per group
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+              uint32_t w[8];
+#pragma unroll
+              for (int e = 0; e < 16; e += 2) {
+                float y0, y1;
+                unpack_f32x2(mul_f32x2(pack_b32x2(oa[c0 + e], oa[c0 + e + 1]), inv2), y0, y1);
+                w[e >> 1] = live ? pack2<BF16>(y0, y1) : 0u;
+              }
+              st_global_v8(orow + cb + c0, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+            }
+            continue;
           }
 #pragma unroll
           for (int c0 = 0; c0 < 64; c0 += 16) {
