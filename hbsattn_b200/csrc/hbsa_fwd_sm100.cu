@@ -21,9 +21,10 @@
 //    One thread issues every MMA; because tcgen05.mma instructions of one thread execute in issue
 //    order, S(t+2) is issued right behind P V(t) into the buffer that P(t) occupies without waiting
 //    for P V(t) to complete (HBSA_STRICT_TCGEN05 builds wait and fence instead; they exist to check this
-//    ordering bit for bit).  Issuing one tcgen05.mma occupies its thread for 70 to 100 clocks whatever the
-//    shape (measured), so the twelve instructions of a 64-row tile are about half of the tile period: the thread
-//    looks for new inputs between the two products only, and its polling loop is kept to one probe per turn.
+//    ordering bit for bit).  The issuing thread blocks until the tensor pipe's queue takes an instruction, so the
+//    twelve instructions of a 64-row tile occupy it for as long as the products of both resident CTAs occupy the
+//    pipe (measured: about half of the tile period); it looks for new inputs between the two products only,
+//    and its polling loop is kept to one probe per turn.
 //  * Online softmax in registers, one thread per row: tcgen05.ld of the tile's <= 64 columns, in-place
 //    -inf masking on diagonal / ragged tiles, exp2 with the scale folded in, fp32 row sum; no shuffles
 //    and no shared-memory exchange.  The exponentials of a tile run against the reference maximum of the
@@ -35,7 +36,9 @@
 //
 // Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp id), warp 4 work
 // fetch + TMA producer, warp 5 TMEM allocator + MMA issuer.  TMEM (256 columns): S0 [0,64), S1 [64,128),
-// O [128,256).
+// O [128,256).  The kernel is instantiated for tiles of 64, 128 and 256 head dimensions; other head dimensions
+// (multiples of 8) run on the next larger one with the surplus columns zero-filled by the TMA boxes.  At 256 a CTA
+// takes 512 TMEM columns (O [128,384)) and 192 KB of shared memory, i.e. one CTA per SM.
 //
 // mbarriers.  T counts K/V tiles over the whole life of the CTA, I counts published items, Iq those
 // of them that have tiles.  Two-entry barrier arrays are indexed by the low bit of the count and
